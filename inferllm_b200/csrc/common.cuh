@@ -1,0 +1,65 @@
+// Shared device helpers of the sm_100a kernels: element conversion, warp and block
+// reductions with a fixed order (so that a row's result never depends on what else is in
+// the launch), and the C ABI conventions.
+//
+// C ABI: every entry point is `extern "C" int illm_<name>(..., void* stream)`; it returns 0
+// or a cudaError_t of the launch, never aborts.  dtype codes: 0 = float32, 1 = bfloat16.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define ILLM_F32 0
+#define ILLM_BF16 1
+#define ILLM_ERR_BAD_ARG 10001  // outside cudaError_t's range: an argument the kernel refuses
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the block; every thread gets the result.  `scratch` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarp = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarp) ? scratch[lane] : 0.f;
+    return warp_sum(t);
+}
+
+// 16-byte loads of 8 bf16 or 4 float into float registers.
+__device__ __forceinline__ void load8(const bf16* p, float* f) {
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        float2 t = __bfloat1622float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+__device__ __forceinline__ void load8(const float* p, float* f) {
+    float4 a = *reinterpret_cast<const float4*>(p);
+    float4 b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+static inline int illm_launch_status() { return (int)cudaGetLastError(); }

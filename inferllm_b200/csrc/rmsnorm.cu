@@ -1,0 +1,93 @@
+// Residual add + RMSNorm in one pass over the row.
+//
+//   x = resid[r] (+ delta[r]);  resid[r] = x (if write_resid);
+//   y[i] = (x * rsqrt(mean(x^2) + eps)) * w
+//
+// The reference runs three launches for this (the add src/kern/gpu/kernel_gpu.cu:183-258,
+// the norm :260-294 with one warp per row, the weight multiply :33-75), formula
+// src/kern/naive/naive.cpp:186-207.  The residual stream is float32 in every mode; the sum
+// of squares, the scale and the product with the weight are float32 and y is rounded once.
+// `rows` (optional) gathers: block i reads row rows[i] and writes output row i, which is how
+// the final norm touches only the positions whose logits are wanted.
+// One block per row; the row is kept in shared memory between the two passes, so H is
+// bounded by the shared memory a block can have (checked on the host side of the call).
+#include "common.cuh"
+
+template <typename TA, typename TW>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restrict__ delta,
+                                   const TW* __restrict__ w, TA* __restrict__ y,
+                                   const int* __restrict__ rows, int H, float eps,
+                                   int write_resid) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* x = resid + (size_t)r * H;
+    const TA* dl = delta ? delta + (size_t)r * H : nullptr;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = x[c];
+        if (dl) v += to_f32(dl[c]);
+        row[c] = v;
+        ss += v * v;
+    }
+    if (dl && write_resid)
+        for (int c = threadIdx.x; c < H; c += blockDim.x) x[c] = row[c];
+    ss = block_sum(ss, scratch);
+    const float scale = rsqrtf(ss / (float)H + eps);
+    TA* o = y + (size_t)blockIdx.x * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x)
+        o[c] = from_f32<TA>((row[c] * scale) * to_f32(w[c]));
+}
+
+template <typename TA, typename TW>
+static int launch(float* resid, const void* delta, const void* w, void* y, const int* rows,
+                  int n_rows, int H, float eps, int write_resid, cudaStream_t s) {
+    size_t smem = (size_t)H * sizeof(float);
+    if (smem > 200 * 1024) return ILLM_ERR_BAD_ARG;
+    auto kern = add_rmsnorm_kernel<TA, TW>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+    kern<<<n_rows, threads, smem, s>>>(resid, (const TA*)delta, (const TW*)w, (TA*)y, rows, H, eps,
+                                       write_resid);
+    return illm_launch_status();
+}
+
+extern "C" int illm_add_rmsnorm(float* resid, const void* delta, const void* w, int w_dtype,
+                                void* y, int act_dtype, const int* rows, int n_rows, int H,
+                                float eps, int write_resid, void* stream) {
+    if (n_rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == ILLM_BF16 && w_dtype == ILLM_BF16)
+        return launch<bf16, bf16>(resid, delta, w, y, rows, n_rows, H, eps, write_resid, s);
+    if (act_dtype == ILLM_BF16 && w_dtype == ILLM_F32)
+        return launch<bf16, float>(resid, delta, w, y, rows, n_rows, H, eps, write_resid, s);
+    if (act_dtype == ILLM_F32 && w_dtype == ILLM_F32)
+        return launch<float, float>(resid, delta, w, y, rows, n_rows, H, eps, write_resid, s);
+    if (act_dtype == ILLM_F32 && w_dtype == ILLM_BF16)
+        return launch<float, bf16>(resid, delta, w, y, rows, n_rows, H, eps, write_resid, s);
+    return ILLM_ERR_BAD_ARG;
+}
+
+// resid[r] += delta[r] without a norm (flushes a pending addition of the residual stream).
+template <typename TA>
+__global__ void residual_add_kernel(float* __restrict__ resid, const TA* __restrict__ delta, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) resid[i] += to_f32(delta[i]);
+}
+
+extern "C" int illm_residual_add(float* resid, const void* delta, int act_dtype, long long n,
+                                 void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    unsigned blocks = (unsigned)((n + 255) / 256);
+    if (act_dtype == ILLM_BF16)
+        residual_add_kernel<bf16><<<blocks, 256, 0, s>>>(resid, (const bf16*)delta, (size_t)n);
+    else if (act_dtype == ILLM_F32)
+        residual_add_kernel<float><<<blocks, 256, 0, s>>>(resid, (const float*)delta, (size_t)n);
+    else
+        return ILLM_ERR_BAD_ARG;
+    return illm_launch_status();
+}

@@ -1,0 +1,39 @@
+// Gated activation of the feed-forward: out[t, i] = silu(gu[t, i]) * gu[t, I + i], where the
+// packed projection holds the gate in its first I columns and the up projection in the next I.
+// silu(x) = x / (1 + exp(-x)) as in the reference (src/kern/gpu/kernel_gpu.cu:183-258 runs it
+// as two launches, Silu and Mul; formula src/kern/naive/naive.cpp:80-89), in float32.
+#include "common.cuh"
+
+template <typename TA>
+__global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I) {
+    const int t = blockIdx.y;
+    const TA* g = gu + (size_t)t * 2 * I;
+    const TA* u = g + I;
+    TA* o = out + (size_t)t * I;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < I; c += gridDim.x * blockDim.x) {
+        float a = to_f32(g[c]);
+        float b = to_f32(u[c]);
+        float sv = a / (1.0f + expf(-a));
+        o[c] = from_f32<TA>(sv * b);
+    }
+}
+
+extern "C" int illm_swiglu(const void* gu, void* out, int act_dtype, int T, int I, void* stream) {
+    if (T <= 0 || I <= 0) return 0;
+    if (T > 65535 * 32) return ILLM_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    // grid.y is limited to 65535: fold larger T into several launches
+    for (int t0 = 0; t0 < T; t0 += 65535) {
+        int n = T - t0 < 65535 ? T - t0 : 65535;
+        dim3 grid((I + 255) / 256 > 64 ? 64 : (I + 255) / 256, n);
+        if (act_dtype == ILLM_BF16)
+            swiglu_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)gu + (size_t)t0 * 2 * I,
+                                                     (bf16*)out + (size_t)t0 * I, I);
+        else if (act_dtype == ILLM_F32)
+            swiglu_kernel<float><<<grid, 256, 0, s>>>((const float*)gu + (size_t)t0 * 2 * I,
+                                                      (float*)out + (size_t)t0 * I, I);
+        else
+            return ILLM_ERR_BAD_ARG;
+    }
+    return illm_launch_status();
+}

@@ -1,0 +1,227 @@
+"""The engine: a model, its cache, and the one step function that everything else drives.
+
+`Engine.step(items)` runs the tokens it is given, as one batch, from the cache that earlier
+steps left, and returns the float32 logits at the wanted places.  A step may hold prompts of
+unequal lengths (all their tokens at once), single next tokens, or both; a sequence's start
+position is the cache's own record of its length.  The generation loop, the command line, the
+Python entry point and `bin/trace_run` all go through this function.
+
+The reference's counterpart is `Graph::execute(tokens, logits, nr_past, prefill)`
+(src/core/graph.cpp:166-197): one sequence, the caller passes the past length, logits of the
+last token only or none at all.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheError, SequenceCache
+from ..parts.base import Runtime
+from ..registry import config_from_folder, get_architecture
+from ..weights import init_random_weights, load_model_weights
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "fp32": torch.float32}
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+@dataclass
+class EngineOptions:
+    dtype: str = "bfloat16"        # "bfloat16": serving kernels; "float32": everything in true 32-bit
+    device_id: int = 0
+    max_tokens: int = 4096         # tokens that live sequences may hold together (sizes the cache)
+    max_seq_len: Optional[int] = None   # longest sequence; default the model's max positions
+    max_batch: Optional[int] = None     # slots; default max_tokens / page_size
+    page_size: int = 64
+
+
+@dataclass
+class Limits:
+    max_batch: int      # sequences that can be live together (slots)
+    num_pages: int      # pages of the cache
+    page_size: int
+    max_seq_len: int
+
+
+@dataclass
+class StepItem:
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=list)  # places among `tokens` whose logits are asked for
+
+
+class StepContext:
+    """Device-side description of one step, shared by all parts.
+
+    ids, token_pos, token_seq : int32 [T]   token id, absolute position, index of its sequence
+    want_rows : int32 [K]   rows (among the T tokens) whose logits are wanted
+    slots, seq_lens, cu_q : int32 [B], [B], [B+1]   slot, length after the step, token offsets
+    """
+
+    def __init__(self, engine, plan, ids_host, want_rows_host):
+        cache, dev = engine.cache, engine.rt.device
+        B = len(plan.slots)
+        q = np.asarray(plan.q_lens, dtype=np.int64)
+        past = np.asarray(plan.past, dtype=np.int64)
+        T = int(q.sum())
+        cu = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(q, out=cu[1:])
+        token_seq = np.repeat(np.arange(B), q)
+        token_pos = np.arange(T) - np.repeat(cu[:-1], q) + np.repeat(past, q)
+        parts = [np.asarray(ids_host, dtype=np.int32), token_pos.astype(np.int32),
+                 token_seq.astype(np.int32), np.asarray(want_rows_host, dtype=np.int32),
+                 np.asarray(plan.slots, dtype=np.int32), (past + q).astype(np.int32),
+                 cu.astype(np.int32)] + [t.reshape(-1) for t in plan.tables]
+        offs, total = [], 0
+        for p in parts:
+            offs.append(total)
+            total += (p.size + 3) // 4 * 4  # keep every array 16-byte aligned
+        buf = engine._upload(parts, offs, total)
+
+        def view(i):
+            return buf[offs[i]:offs[i] + parts[i].size]
+
+        self.T, self.B = T, B
+        self.ids, self.token_pos, self.token_seq = view(0), view(1), view(2)
+        self.want_rows, self.slots, self.seq_lens, self.cu_q = view(3), view(4), view(5), view(6)
+        self.tables = [view(7 + i).view(B, cache.width) for i in range(len(plan.tables))]
+        self.q_lens, self.past = list(plan.q_lens), list(plan.past)
+        self.max_q = int(q.max())
+        self.max_len = int((past + q).max())
+        self.is_decode = self.max_q == 1
+        self.err = engine.err
+        self._cache = cache
+
+    def cache_view(self, entry: int, writes: bool = True):
+        if entry not in self._cache.where:
+            return None
+        kind, gi = self._cache.group_of(entry)
+        if kind == "kv":
+            view = self._cache.kv_view(entry, self.tables[gi])
+            view.writes = writes
+            return view
+        return self._cache.state_view(entry, self.slots)
+
+
+class Engine:
+    def __init__(self, config, options: EngineOptions):
+        if options.dtype not in _DTYPES:
+            raise EngineError(f"dtype '{options.dtype}' is not supported (bfloat16 or float32)")
+        self.config = config
+        self.options = options
+        self.rt = self._make_runtime(options)
+        dev = self.rt.device
+        self.model = get_architecture(config.architecture).build_model(config, self.rt)
+        spec = self.model.spec
+        self.vocab_size = spec.vocab_size
+        max_seq = min(options.max_seq_len or spec.max_positions, spec.max_positions)
+        ps = options.page_size
+        num_pages = max(1, -(-options.max_tokens // ps))
+        num_slots = options.max_batch or num_pages
+        self.cache = SequenceCache(self.model.cache_requests(), num_slots, num_pages, ps, max_seq,
+                                   self.rt)
+        self.err = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._stage = None
+        self._staging_busy = None
+        self.loaded = False
+
+    def _make_runtime(self, options: EngineOptions) -> Runtime:
+        if not torch.cuda.is_available():
+            raise EngineError("inferllm_b200 needs a CUDA device: there is no CPU path")
+        from ..kernels.lib import load
+        load()  # fail here, loudly, if the kernels cannot be built or loaded
+        dev = torch.device("cuda", options.device_id)
+        torch.cuda.set_device(dev)
+        return Runtime(dev, _DTYPES[options.dtype], options.page_size)
+
+    # ---- construction
+
+    @classmethod
+    def from_folder(cls, folder: str, options: EngineOptions, model_name: Optional[str] = None):
+        eng = cls(config_from_folder(folder, model_name), options)
+        load_model_weights(eng.model, folder)
+        eng.loaded = True
+        return eng
+
+    @classmethod
+    def from_config(cls, config, options: EngineOptions, seed: int = 0):
+        """Random weights made on the device, without a file."""
+        eng = cls(config, options)
+        init_random_weights(eng.model, seed)
+        eng.loaded = True
+        return eng
+
+    # ---- sequences
+
+    def new_sequence(self) -> int:
+        return self.cache.alloc_slot()
+
+    def end_sequence(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    def sequence_length(self, slot: int) -> int:
+        return self.cache.seq_len[slot]
+
+    def limits(self) -> Limits:
+        c = self.cache
+        return Limits(c.num_slots, c.num_pages, c.page_size, c.max_seq_len)
+
+    # ---- the step
+
+    def _upload(self, parts, offs, total: int) -> torch.Tensor:
+        """One pinned staging buffer, one asynchronous copy for all of a step's index arrays."""
+        if self._staging_busy is not None:
+            self._staging_busy.synchronize()  # the previous step's copy has left the buffer
+        if self._stage is None or self._stage.numel() < total:
+            self._stage = torch.empty(max(total, 4096), dtype=torch.int32, pin_memory=True)
+        host = self._stage
+        for o, p in zip(offs, parts):
+            host[o:o + p.size] = torch.from_numpy(p)
+        buf = torch.empty(total, dtype=torch.int32, device=self.rt.device)
+        buf.copy_(host[:total], non_blocking=True)
+        self._staging_busy = torch.cuda.Event()
+        self._staging_busy.record()
+        return buf
+
+    def step(self, items: Sequence[StepItem]) -> torch.Tensor:
+        """Run one step; returns float32 logits [number of wanted places, vocab] on the device,
+        in the order of the items and of each item's `want`."""
+        if not self.loaded:
+            raise EngineError("the model has no weights yet")
+        if not items:
+            raise EngineError("a step needs at least one sequence")
+        ids, want_rows, off = [], [], 0
+        for it in items:
+            n = len(it.tokens)
+            if n == 0:
+                raise EngineError(f"slot {it.slot}: a step must bring at least one token")
+            for t in it.tokens:
+                if not 0 <= int(t) < self.vocab_size:
+                    raise EngineError(f"slot {it.slot}: token id {t} is outside the vocabulary "
+                                      f"[0, {self.vocab_size})")
+            for w in it.want:
+                if not 0 <= int(w) < n:
+                    raise EngineError(f"slot {it.slot}: wanted place {w} is outside its {n} tokens")
+                want_rows.append(off + int(w))
+            ids.extend(int(t) for t in it.tokens)
+            off += n
+        plan = self.cache.plan_step([it.slot for it in items], [len(it.tokens) for it in items])
+        ctx = StepContext(self, plan, ids, want_rows)
+        logits = self.model.forward(ctx)
+        self.cache.commit_step(plan)
+        return logits
+
+    def check_device_errors(self) -> None:
+        """Read the kernels' error word (synchronises)."""
+        code = int(self.err.item())
+        if code:
+            self.err.zero_()
+            what = {1: "a token id outside the embedding table", 2: "a cache write to a page that "
+                    "the sequence does not hold", 3: "a position beyond the position table"}
+            raise EngineError("a kernel reported " + what.get(code, f"error {code}"))

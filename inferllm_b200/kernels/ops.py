@@ -1,0 +1,223 @@
+"""Python faces of the CUDA kernels: argument checks, output allocation, the launch.
+
+Every function takes CUDA tensors, launches on torch's current stream and returns
+without synchronising.  A size that a kernel cannot take is refused here with a
+`KernelError` that names it; nothing falls back to another implementation, except that
+the plain matrix product of the bfloat16 mode is the library's (cuBLAS through
+`torch.mm`), as the reference's is (cublasSgemm, src/kern/gpu/kernel_gpu.cu:420-435).
+"""
+from __future__ import annotations
+
+import torch
+
+from .lib import load
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+MAX_HEAD_DIM_GENERIC = 256
+MAX_NORM_WIDTH = 200 * 1024 // 4
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code, what):
+    if code != 0:
+        if code == 10001:
+            raise KernelError(f"{what}: the kernel refused its arguments")
+        raise KernelError(f"{what}: CUDA error {code}")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _need(t, name, dtype=None, dim=None):
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor: inferllm_b200 has no CPU path")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, found {t.dtype}")
+    if dim is not None and t.dim() != dim:
+        raise KernelError(f"{name} must have {dim} dimensions, found shape {tuple(t.shape)}")
+
+
+def act_code(dtype):
+    if dtype not in _DT:
+        raise KernelError(f"unsupported dtype {dtype}: the kernels take float32 and bfloat16")
+    return _DT[dtype]
+
+
+def embedding(ids, table, err):
+    """ids int32 [T], table [V, H] (float32 or bfloat16) -> float32 [T, H]."""
+    _need(ids, "ids", torch.int32, 1)
+    _need(table, "table", None, 2)
+    T, (V, H) = ids.numel(), table.shape
+    out = torch.empty((T, H), dtype=torch.float32, device=ids.device)
+    _check(load().illm_embedding(_ptr(ids), _ptr(table), act_code(table.dtype), _ptr(out), T, H, V,
+                                 _ptr(err), _stream()), "embedding")
+    return out
+
+
+def add_rmsnorm(resid, delta, weight, eps, out_dtype, rows=None, write_resid=True):
+    """y = rmsnorm(resid (+ delta)) * weight; resid is updated in place when `write_resid`.
+    `rows` (int32 [K]) gathers: only those rows are normed and y is [K, H]."""
+    _need(resid, "resid", torch.float32, 2)
+    H = resid.shape[1]
+    if H > MAX_NORM_WIDTH:
+        raise KernelError(f"rmsnorm: width {H} exceeds the {MAX_NORM_WIDTH} that one block's "
+                          "shared memory holds")
+    if delta is not None:
+        _need(delta, "delta", out_dtype, 2)
+        if delta.shape != resid.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} does not match resid {tuple(resid.shape)}")
+    _need(weight, "norm weight", None, 1)
+    if weight.numel() != H:
+        raise KernelError(f"norm weight has {weight.numel()} elements, the rows have {H}")
+    n = resid.shape[0] if rows is None else rows.numel()
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+    y = torch.empty((n, H), dtype=out_dtype, device=resid.device)
+    _check(load().illm_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(weight), act_code(weight.dtype),
+                                   _ptr(y), act_code(out_dtype), _ptr(rows), n, H, float(eps),
+                                   1 if write_resid else 0, _stream()), "add_rmsnorm")
+    return y
+
+
+def residual_add(resid, delta):
+    _need(resid, "resid", torch.float32)
+    _need(delta, "delta")
+    if delta.shape != resid.shape:
+        raise KernelError("residual_add: shapes differ")
+    _check(load().illm_residual_add(_ptr(resid), _ptr(delta), act_code(delta.dtype), resid.numel(),
+                                    _stream()), "residual_add")
+
+
+def swiglu(gu):
+    """gu [T, 2I] = [gate | up] -> silu(gate) * up, [T, I]."""
+    _need(gu, "gate_up", None, 2)
+    T, I2 = gu.shape
+    out = torch.empty((T, I2 // 2), dtype=gu.dtype, device=gu.device)
+    _check(load().illm_swiglu(_ptr(gu), _ptr(out), act_code(gu.dtype), T, I2 // 2, _stream()), "swiglu")
+    return out
+
+
+def rope_kv_write(qkv, cos_sin, rot_dim, token_pos, token_seq, block_table, k_cache, v_cache,
+                  n_heads, n_kv_heads, head_dim, page_size, write_kv, err):
+    """Rotate Q (and K) of the packed projection in place and store K, V in the cache pages.
+    `cos_sin` float32 [positions, rot_dim/2, 2] or None with rot_dim 0."""
+    _need(qkv, "qkv", None, 2)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim:
+        raise KernelError(f"qkv width {qkv.shape[1]} is not (heads + 2 kv heads) * head_dim")
+    for name, t in (("token_pos", token_pos), ("token_seq", token_seq)):
+        _need(t, name, torch.int32, 1)
+    _need(block_table, "block_table", torch.int32, 2)
+    if write_kv:
+        _need(k_cache, "k_cache", qkv.dtype, 4)
+        _need(v_cache, "v_cache", qkv.dtype, 4)
+        if tuple(k_cache.shape[1:]) != (n_kv_heads, page_size, head_dim):
+            raise KernelError(f"cache pages {tuple(k_cache.shape)} do not match "
+                              f"[pages, {n_kv_heads}, {page_size}, {head_dim}]")
+    n_pos = 0
+    if rot_dim:
+        _need(cos_sin, "cos_sin", torch.float32, 3)
+        if cos_sin.shape[1] != rot_dim // 2:
+            raise KernelError("cos_sin table does not match rot_dim")
+        n_pos = cos_sin.shape[0]
+    _check(load().illm_rope_kv_write(
+        _ptr(qkv), _ptr(cos_sin) if rot_dim else None, _ptr(token_pos), _ptr(token_seq),
+        _ptr(block_table), block_table.shape[1], _ptr(k_cache) if write_kv else None,
+        _ptr(v_cache) if write_kv else None, act_code(qkv.dtype), T, n_heads, n_kv_heads, head_dim,
+        rot_dim, page_size, 1 if write_kv else 0, n_pos, _ptr(err), _stream()), "rope_kv_write")
+
+
+def attention_generic(qkv, k_cache, v_cache, block_table, token_pos, token_seq, n_heads,
+                      n_kv_heads, head_dim, page_size, window, scale):
+    """Attention of each token (query heads in the first n_heads*head_dim columns of `qkv`)
+    over its sequence's cache pages; returns [T, n_heads*head_dim]."""
+    if head_dim % 8 or head_dim > MAX_HEAD_DIM_GENERIC:
+        raise KernelError(f"attention: head size {head_dim} is not supported (multiples of 8 up to "
+                          f"{MAX_HEAD_DIM_GENERIC})")
+    if n_heads % n_kv_heads:
+        raise KernelError("attention: heads must be a multiple of kv heads")
+    _need(qkv, "qkv", None, 2)
+    _need(k_cache, "k_cache", qkv.dtype, 4)
+    _need(v_cache, "v_cache", qkv.dtype, 4)
+    T = qkv.shape[0]
+    out = torch.empty((T, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    _check(load().illm_attention_generic(
+        _ptr(qkv), qkv.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+        block_table.shape[1], _ptr(token_pos), _ptr(token_seq), _ptr(out), act_code(qkv.dtype), T,
+        n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), _stream()),
+        "attention_generic")
+    return out
+
+
+def attention(qkv, kv, ctx, n_heads, n_kv_heads, head_dim, window, scale):
+    """Attention of the step's tokens over the cache entry `kv` (a KVView): picks the kernel
+    for the dtype, head size and kind of step."""
+    return attention_generic(qkv, kv.k, kv.v, kv.block_table, ctx.token_pos, ctx.token_seq,
+                             n_heads, n_kv_heads, head_dim, kv.page_size, window, scale)
+
+
+def gemm_f32(x, w):
+    """float32 x [M, K] . w [N, K]^T -> [M, N] with float32 FMA accumulation."""
+    _need(x, "x", torch.float32, 2)
+    _need(w, "w", torch.float32, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"gemm: x is [{M}, {K}] but w is {tuple(w.shape)}")
+    out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    for m0 in range(0, M, 65535 * 64):
+        m1 = min(M, m0 + 65535 * 64)
+        _check(load().illm_gemm_f32_nt(_ptr(x[m0:m1]), _ptr(w), _ptr(out[m0:m1]), m1 - m0, N, K, K, K,
+                                       N, _stream()), "gemm_f32")
+    return out
+
+
+def linear(x, w, out_dtype=None):
+    """x [M, K] . w [N, K]^T.  float32: the package's own FMA kernel.  bfloat16: the library
+    product with float32 accumulation, rounded to bfloat16 or kept float32 (`out_dtype`)."""
+    if x.dtype == torch.float32:
+        return gemm_f32(x, w)
+    _need(x, "x", torch.bfloat16, 2)
+    _need(w, "w", torch.bfloat16, 2)
+    if out_dtype == torch.float32:
+        return torch.mm(x, w.t(), out_dtype=torch.float32)
+    return torch.mm(x, w.t())
+
+
+def argmax(logits):
+    """float32 [B, V] -> int32 [B], the lowest id among equal maxima."""
+    _need(logits, "logits", torch.float32, 2)
+    B, V = logits.shape
+    out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    _check(load().illm_argmax(_ptr(logits), B, V, V, _ptr(out), _stream()), "argmax")
+    return out
+
+
+def sample(logits, uniforms, temp, top_k=0, top_p=1.0, repeat_penalty=1.0, last_tokens=None):
+    """Temperature / repetition penalty / top-k / top-p sampling, one draw per row.
+    `uniforms` float32 [B] in [0, 1); `last_tokens` int32 [B, n] (-1 pads) or None."""
+    _need(logits, "logits", torch.float32, 2)
+    _need(uniforms, "uniforms", torch.float32, 1)
+    B, V = logits.shape
+    if uniforms.numel() != B:
+        raise KernelError("sample: one uniform number per row is needed")
+    n_last = 0
+    if last_tokens is not None:
+        _need(last_tokens, "last_tokens", torch.int32, 2)
+        n_last = last_tokens.shape[1]
+    z = torch.empty((B, V), dtype=torch.float32, device=logits.device)
+    out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    _check(load().illm_sample(_ptr(logits), B, V, V, _ptr(z), _ptr(last_tokens), n_last, float(temp),
+                              float(repeat_penalty), int(top_k), float(top_p), _ptr(uniforms),
+                              _ptr(out), _stream()), "sample")
+    return out

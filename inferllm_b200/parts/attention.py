@@ -1,0 +1,63 @@
+"""Causal self-attention with grouped heads over the paged cache: the mixer of LLaMA.
+
+Order of operations of the reference's `LlamaAttention::execute` (src/core/op.cpp:348-500):
+Q, K, V projections without bias; position encoding of Q and of the new K rows; K and V go
+into the cache; scores of every query against all cached keys of its sequence, scaled by
+1/sqrt(head size) (:488) and masked causally; softmax; weighted values; then the output
+projection (`AttentionModule`, src/core/graph.h:106-111).  The reference has separate
+[H, H] matrices and one KV head per query head (src/core/op.h:327-332); here the three
+matrices are stacked into one [(heads + 2 kv heads) * d, H] at load so that one product
+feeds the rotation kernel, and the number of KV heads, the head size and an optional window
+are parameters.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..kernels import ops
+from .base import Mixer, PagedKV, TensorDecl, build_part, register_mixer
+
+
+@register_mixer("attention")
+class Attention(Mixer):
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.hidden = int(spec["hidden_size"])
+        self.n_heads = int(spec["n_heads"])
+        self.n_kv_heads = int(spec["n_kv_heads"])
+        self.head_dim = int(spec["head_dim"])
+        self.window = spec.get("window")
+        self.scale = float(spec.get("scale") or 1.0 / math.sqrt(self.head_dim))
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError("attention: n_heads must be a multiple of n_kv_heads")
+        self.position = build_part("position", spec["position"], runtime)
+        if runtime is not None:
+            self.position.prepare()
+        self.w_qkv = None
+        self.w_o = None
+
+    def tensors(self):
+        q, kv = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        return {"q_proj.weight": TensorDecl((q, self.hidden)),
+                "k_proj.weight": TensorDecl((kv, self.hidden)),
+                "v_proj.weight": TensorDecl((kv, self.hidden)),
+                "o_proj.weight": TensorDecl((self.hidden, q))}
+
+    def load(self, tensors):
+        dt = self.rt.dtype
+        self.w_qkv = torch.cat([tensors["q_proj.weight"].to(dt), tensors["k_proj.weight"].to(dt),
+                                tensors["v_proj.weight"].to(dt)], dim=0).contiguous()
+        self.w_o = tensors["o_proj.weight"].to(dt).contiguous()
+
+    def cache_request(self):
+        return PagedKV(self.n_kv_heads, self.head_dim, self.window)
+
+    def forward(self, h, ctx, cache, writes):
+        qkv = ops.linear(h, self.w_qkv)
+        geometry = (self.n_heads, self.n_kv_heads, self.head_dim)
+        self.position.encode_and_store(qkv, geometry, ctx, cache)
+        o = ops.attention(qkv, cache, ctx, self.n_heads, self.n_kv_heads, self.head_dim,
+                          self.window, self.scale)
+        return ops.linear(o, self.w_o)
