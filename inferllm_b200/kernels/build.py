@@ -127,7 +127,7 @@ def build(force: bool = False, verbose: bool = True, extra_flags=()) -> str:
         objs = list(pool.map(compile_one, srcs))
     lib = os.path.join(out, LIB_NAME)
     tmp = lib + f".tmp{os.getpid()}"
-    r = subprocess.run([nvcc, "-shared", "-o", tmp, *objs, "-lcuda"], capture_output=True, text=True)
+    r = subprocess.run([nvcc, "-shared", "-o", tmp, *objs], capture_output=True, text=True)
     if r.returncode != 0:
         raise BuildError(f"link failed:\n{r.stdout}\n{r.stderr}")
     os.replace(tmp, lib)

@@ -1,0 +1,193 @@
+"""The engine against the plain implementation, in every way of cutting the work (GPU).
+
+For each tiny model, in float32 and in bfloat16: each request alone and whole; the last 32
+tokens one by one; batches of unequal lengths whose shorter requests end earlier, one batch
+after another on a cache so small that slots and pages are used again; long decoding; the
+first tokens of a sequence.  In float32 the engine's own results must also be bit-identical
+across the cuttings: its kernels fix the order of every sum per row.
+"""
+import numpy as np
+import pytest
+import torch
+from conftest import TINY, random_prompt
+from util import assert_close, make_engine
+
+from inferllm_b200 import EngineError, StepItem
+from inferllm_b200.cache import CacheError, CacheFull
+
+pytestmark = pytest.mark.gpu
+
+MODELS = ["A", "B", "C", "D"]
+DTYPES = ["float32", "bfloat16"]
+LENGTHS = {"A": [128, 97, 40], "B": [256, 131, 33], "C": [300, 77, 513], "D": [200, 65, 130]}
+
+
+def whole(eng, ids):
+    s = eng.new_sequence()
+    lg = eng.step([StepItem(s, ids, list(range(len(ids))))])
+    eng.end_sequence(s)
+    return lg.cpu().numpy()
+
+
+def tail_one_by_one(eng, ids, tail=32):
+    s = eng.new_sequence()
+    n = len(ids) - tail
+    out = [eng.step([StepItem(s, ids[:n], list(range(n)))])]
+    for t in ids[n:]:
+        out.append(eng.step([StepItem(s, [t], [0])]))
+    eng.end_sequence(s)
+    return torch.cat(out).cpu().numpy()
+
+
+def in_batches(eng, requests, prefill_lens, batches):
+    """Teacher-forced replay: each batch starts together (prompts of unequal lengths in one
+    step), then one token per live request and step; a request leaves when its tokens are used
+    up.  Returns per request the logits at all its positions."""
+    got = {}
+    for batch in batches:
+        slots = {r: eng.new_sequence() for r in batch}
+        lg = eng.step([StepItem(slots[r], requests[r][:prefill_lens[r]], list(range(prefill_lens[r])))
+                       for r in batch]).cpu().numpy()
+        off = 0
+        for r in batch:
+            got[r] = [lg[off:off + prefill_lens[r]]]
+            off += prefill_lens[r]
+        pos = {r: prefill_lens[r] for r in batch}
+        live = [r for r in batch if pos[r] < len(requests[r])]
+        for r in batch:
+            if r not in live:
+                eng.end_sequence(slots[r])
+        while live:
+            lg = eng.step([StepItem(slots[r], [requests[r][pos[r]]], [0]) for r in live]).cpu().numpy()
+            nxt = []
+            for i, r in enumerate(live):
+                got[r].append(lg[i:i + 1])
+                pos[r] += 1
+                if pos[r] < len(requests[r]):
+                    nxt.append(r)
+                else:
+                    eng.end_sequence(slots[r])
+            live = nxt
+    return {r: np.concatenate(v) for r, v in got.items()}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", MODELS)
+def test_whole_and_tail_one_by_one(name, dtype, model_folders, plain_logits):
+    eng = make_engine(model_folders[name], dtype, max_tokens=1024)
+    for i, n in enumerate(LENGTHS[name]):
+        ids = random_prompt(name, n, 100 + i)
+        ref = plain_logits(name, ids)
+        w = whole(eng, ids)
+        assert_close(w, ref, dtype, f"{name} whole n={n}")
+        if n > 40:
+            t = tail_one_by_one(eng, ids)
+            assert_close(t, ref, dtype, f"{name} last 32 one by one n={n}")
+            if dtype == "float32":
+                assert np.array_equal(w, t), "float32: whole and one-by-one logits differ in bits"
+            else:
+                assert_close(t, w, dtype, "whole vs one by one")
+    eng.check_device_errors()
+    eng.cache.check()
+    assert eng.cache.slots.n_free == eng.cache.num_slots
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", MODELS)
+def test_unequal_batches_with_slot_reuse(name, dtype, model_folders, plain_logits):
+    maxpos = TINY[name]["max_position_embeddings"]
+    total = [maxpos, 70, 33, 129 if maxpos > 129 else 90, 64, 1, 65, 100]
+    prefill = [maxpos - 20, 65, 1, 64, 63, 1, 33, 90]
+    reqs = [random_prompt(name, n, 200 + i) for i, n in enumerate(total)]
+    # three slots and few pages: the second and third batch must reuse what the first gave back
+    need = max(sum(-(-total[r] // 64) for r in b) for b in ([0, 1, 2], [3, 4, 5], [6, 7]))
+    eng = make_engine(model_folders[name], dtype, max_tokens=64 * need, max_batch=3)
+    got = in_batches(eng, reqs, prefill, [[0, 1, 2], [3, 4, 5], [6, 7]])
+    for r, ids in enumerate(reqs):
+        assert_close(got[r], plain_logits(name, ids), dtype, f"{name} request {r} in batches")
+    if dtype == "float32":
+        for r in (0, 3, 7):
+            assert np.array_equal(got[r], whole(eng, reqs[r])), \
+                f"float32: request {r} differs between a batch and alone"
+    eng.check_device_errors()
+    eng.cache.check()
+    assert eng.cache.pages_free() == [need]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_and_first_tokens(dtype, model_folders, plain_logits):
+    """A one-token prompt decoded for hundreds of steps across page borders, next to a second
+    sequence that starts at the same time and ends early."""
+    name = "D"
+    ids = random_prompt(name, 400, 7)
+    other = random_prompt(name, 9, 8)
+    eng = make_engine(model_folders[name], dtype, max_tokens=64 * 8, max_batch=2)
+    got = in_batches(eng, [ids, other], [1, 2], [[0, 1]])
+    ref = plain_logits(name, ids)
+    assert_close(got[0][:8], ref[:8], dtype, "first tokens")
+    assert_close(got[0], ref, dtype, "long decoding")
+    assert_close(got[1], plain_logits(name, other), dtype, "short neighbour")
+    eng.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_wanted_places_and_padding_free_batches(dtype, model_folders, plain_logits):
+    name = "B"
+    a, b, c = (random_prompt(name, n, 300 + n) for n in (50, 3, 17))
+    eng = make_engine(model_folders[name], dtype, max_tokens=512)
+    sa, sb, sc = (eng.new_sequence() for _ in range(3))
+    lg = eng.step([StepItem(sa, a, [49, 0]), StepItem(sb, b, []), StepItem(sc, c, [16])]).cpu().numpy()
+    assert lg.shape == (3, TINY[name]["vocab_size"])
+    assert_close(lg[0], plain_logits(name, a)[49], dtype)
+    assert_close(lg[1], plain_logits(name, a)[0], dtype)
+    assert_close(lg[2], plain_logits(name, c)[16], dtype)
+    none = eng.step([StepItem(sb, [7], [])])
+    assert tuple(none.shape) == (0, TINY[name]["vocab_size"])
+    # the request that asked for nothing still advanced: its next logits see all four tokens
+    lg = eng.step([StepItem(sb, [9], [0])]).cpu().numpy()
+    assert_close(lg[0], plain_logits(name, b + [7, 9])[-1], dtype)
+    for s in (sa, sb, sc):
+        eng.end_sequence(s)
+
+
+def test_result_does_not_depend_on_the_slot_or_on_old_cache_contents(model_folders):
+    """float32, bit for bit: a request gives the same logits in a fresh cache, in another slot,
+    and in pages that other requests have filled before."""
+    name = "A"
+    ids = random_prompt(name, 100, 1)
+    eng = make_engine(model_folders[name], "float32", max_tokens=64 * 6, max_batch=3)
+    first = tail_one_by_one(eng, ids)
+    junk = [eng.new_sequence() for _ in range(2)]
+    eng.step([StepItem(junk[0], random_prompt(name, 128, 2), []),
+              StepItem(junk[1], random_prompt(name, 90, 3), [])])
+    eng.end_sequence(junk[0])          # slot 0 and its pages go back, slot 1 stays live
+    s = eng.new_sequence()
+    lg = [eng.step([StepItem(s, ids[:68], list(range(68)))])]
+    for t in ids[68:]:
+        lg.append(eng.step([StepItem(s, [t], [0]), StepItem(junk[1], [5], [])])[:1])
+    again = torch.cat(lg).cpu().numpy()
+    assert np.array_equal(first, again)
+    eng.check_device_errors()
+
+
+def test_refusals(model_folders):
+    eng = make_engine(model_folders["A"], "float32", max_tokens=128, max_batch=2)
+    s = eng.new_sequence()
+    with pytest.raises(EngineError, match="vocabulary"):
+        eng.step([StepItem(s, [256], [])])
+    with pytest.raises(EngineError, match="wanted place"):
+        eng.step([StepItem(s, [1, 2], [2])])
+    with pytest.raises(EngineError, match="at least one token"):
+        eng.step([StepItem(s, [], [])])
+    with pytest.raises(CacheError, match="maximum sequence length"):
+        eng.step([StepItem(s, [1] * 129, [])])
+    t = eng.new_sequence()
+    eng.step([StepItem(s, [1] * 100, [])])
+    with pytest.raises(CacheFull):
+        eng.step([StepItem(t, [1] * 10, [])])     # two pages are taken, the cache has two
+    assert eng.sequence_length(t) == 0
+    with pytest.raises(CacheFull):
+        eng.new_sequence()
+    eng.end_sequence(s)
+    eng.step([StepItem(t, [1] * 10, [9])])
+    eng.check_device_errors()

@@ -1,0 +1,139 @@
+"""Generation through the entry point and the command line against the plain implementation's
+greedy continuation, and the sampling options end to end (GPU)."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import plain_llama as plain
+import pytest
+from conftest import ROOT, TINY, random_prompt
+
+from inferllm_b200 import Model, ModelConfig
+from inferllm_b200.sampling import uniform_for
+
+pytestmark = pytest.mark.gpu
+
+
+def load(folder, dtype, **kw):
+    m = Model(ModelConfig(compt_type=dtype, nr_ctx=kw.pop("nr_ctx", 256), **kw))
+    m.load(folder)
+    return m
+
+
+@pytest.mark.parametrize("name,lens,n_new", [("A", [5, 9, 16], 8), ("B", [1, 7, 23, 40], 12)])
+def test_greedy_generation_matches_plain(name, lens, n_new, model_folders, plain_models):
+    cfg, w = plain_models[name]
+    prompts = [random_prompt(name, n, 40 + n) for n in lens]
+    want = [plain.greedy_generate(cfg, w, p, n_new) for p in prompts]
+    m = load(model_folders[name], "float32", nr_ctx=TINY[name]["max_position_embeddings"], max_tokens=512)
+    m.init(top_k=0, top_p=1.0, temp=0.0, repeat_penalty=1.0, repeat_last_n=0, seed=0, end_token=-1)
+    res = m.generate(prompts, max_new_tokens=n_new, stop_ids=[])
+    assert res.tokens == want and res.finish == ["length"] * len(lens)
+    # bfloat16 may turn a near-tie the other way; the first tokens of every request must agree
+    mb = load(model_folders[name], "bfloat16", nr_ctx=TINY[name]["max_position_embeddings"], max_tokens=512)
+    mb.init(0, 1.0, 0.0, 1.0, 0, 0, -1)
+    got = mb.generate(prompts, max_new_tokens=n_new, stop_ids=[]).tokens
+    assert sum(g == w_ for g, w_ in zip(got, want)) >= len(lens) - 1
+    assert all(g[0] == w_[0] for g, w_ in zip(got, want))
+
+
+def test_stop_token_ends_early_and_batches_follow_each_other(model_folders, plain_models):
+    name = "A"
+    cfg, w = plain_models[name]
+    prompts = [random_prompt(name, n, 70 + n) for n in (30, 4, 11, 19, 2)]
+    free_run = [plain.greedy_generate(cfg, w, p, 10) for p in prompts]
+    stop = free_run[1][3]                       # request 1 stops at its 4th token
+    want = [plain.greedy_generate(cfg, w, p, 10, stop_ids=[stop]) for p in prompts]
+    m = load(model_folders[name], "float32", nr_ctx=128, max_tokens=64 * 2, max_batch=2)   # 2 at a time
+    m.init(0, 1.0, 0.0, 1.0, 0, 0, end_token=stop)
+    res = m.generate(prompts, max_new_tokens=10)
+    assert res.tokens == want
+    assert res.batches == [[0, 1], [2, 3], [4]]
+    assert res.finish[1] == "stop" and len(res.tokens[1]) <= 4
+    m.engine.cache.check()
+    assert m.engine.cache.slots.n_free == 2
+
+
+def test_single_conversation_api_of_the_reference(model_folders, plain_models):
+    """load / init / prefill / decode / decode_iter / get_remain_token / reset_token."""
+    name = "B"
+    cfg, w = plain_models[name]
+    system, user = random_prompt(name, 12, 1), random_prompt(name, 5, 2)
+    want = plain.greedy_generate(cfg, w, system + user, 6)
+    m = load(model_folders[name], "float32", nr_ctx=64)
+    m.init(0, 1.0, 0.0, 1.0, 0, 0, end_token=-1)
+    assert m.get_remain_token() == 64
+    m.prefill(system)
+    assert m.get_remain_token() == 64 - 12
+    got = [m.decode(user)]
+    for _ in range(5):
+        got.append(m.decode_iter())
+    assert got == want
+    assert m.get_remain_token() == 64 - 12 - 5 - 5
+    assert "Total Model Compute Token:  5" in m.decode_summary()
+    m.reset_token()
+    assert m.get_remain_token() == 64
+    assert m.decode(system + user) == want[0]
+
+
+def test_temperature_sampling_is_reproducible_and_batch_independent(model_folders):
+    name = "B"
+    prompts = [random_prompt(name, n, 90 + n) for n in (1, 7, 23, 40)]
+    m = load(model_folders[name], "float32", nr_ctx=256, max_tokens=1024)
+    m.init(top_k=0, top_p=1.0, temp=0.8, repeat_penalty=1.0, repeat_last_n=0, seed=123, end_token=-1)
+    a = m.generate(prompts, max_new_tokens=12, stop_ids=[]).tokens
+    b = m.generate(prompts, max_new_tokens=12, stop_ids=[]).tokens
+    assert a == b
+    assert len({tuple(t) for t in a}) == 4
+    m.init(0, 1.0, 0.8, 1.0, 0, seed=124, end_token=-1)
+    assert m.generate(prompts, max_new_tokens=12, stop_ids=[]).tokens != a
+    # request 0 alone draws what it drew in the batch: its random numbers are keyed by
+    # (seed, request, step) and its logits do not depend on the batch
+    m.init(0, 1.0, 0.8, 1.0, 0, seed=123, end_token=-1)
+    assert m.generate(prompts[:1], max_new_tokens=12, stop_ids=[]).tokens[0] == a[0]
+    assert 0.0 <= uniform_for(1, 2, 3) < 1.0 and uniform_for(1, 2, 3) != uniform_for(1, 2, 4)
+
+
+def test_repeat_penalty_changes_greedy_choice(model_folders, plain_models):
+    name = "A"
+    cfg, w = plain_models[name]
+    p = random_prompt(name, 20, 5)
+    logits = plain.forward(cfg, w, p)[-1]
+    top = int(np.argmax(logits))
+    m = load(model_folders[name], "float32", nr_ctx=128)
+    m.init(top_k=0, top_p=1.0, temp=0.0, repeat_penalty=1e6, repeat_last_n=64, seed=0, end_token=-1)
+    # the prompt's own tokens are penalised; put the favourite into the prompt and it loses
+    tok = m.generate([p + [top]], max_new_tokens=1, stop_ids=[]).tokens[0][0]
+    lg2 = plain.forward(cfg, w, p + [top])[-1]
+    ids, _ = plain.sample_distribution(lg2, p + [top], 1e6, 1, 1.0, 1.0)
+    assert tok == int(ids[0]) and tok not in set(p + [top]) or lg2[tok] < 0
+
+
+def test_command_line(model_folders, plain_models, tmp_path):
+    name = "A"
+    cfg, w = plain_models[name]
+    prompts = [random_prompt(name, n, 60 + n) for n in (6, 13)]
+    want = [plain.greedy_generate(cfg, w, p, 5) for p in prompts]
+    args = [sys.executable, os.path.join(ROOT, "bin", "llama"), "-m", model_folders[name], "-g", "GPU", "-d", "float32",
+            "-c", "128", "-n", "5", "--temp", "0", "--top_k", "0", "--top_p", "1", "--repeat_penalty", "1",
+            "--no-stop", "-s", "1"]
+    for p in prompts:
+        args += ["--prompt-ids", ",".join(map(str, p))]
+    r = subprocess.run(args, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("[")]
+    got = [[int(t) for t in ln.split(": ")[1].split(",")] for ln in lines]
+    assert got == want and "decode:" in r.stderr
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llama"), "-m", model_folders[name], "-g", "CPU",
+                        "--prompt-ids", "1"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 2 and "CPU" in r.stderr
+    # random weights from a config file, no model folder
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(TINY["B"]))
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llama"), "--config", str(cfg_file),
+                        "--random-weights", "4", "--random-prompts", "3,8", "-n", "4", "-c", "64", "-s", "2"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    assert len([ln for ln in r.stdout.splitlines() if ln.startswith("[")]) == 2

@@ -1,0 +1,137 @@
+"""Decisions of the generation loop, with stand-ins for the engine and the sampler (no GPU)."""
+import pytest
+
+from inferllm_b200.engine import Limits, RequestTooLong, generate, plan_batches
+
+
+class FakeBackend:
+    """Keeps the bookkeeping a real engine would and returns 'logits' that simply name, for each
+    wanted place, (slot, position) so that a scripted chooser can answer."""
+
+    def __init__(self, max_batch=2, num_pages=8, page_size=4, max_seq_len=16):
+        self.lim = Limits(max_batch, num_pages, page_size, max_seq_len)
+        self.free = list(range(max_batch))[::-1]
+        self.len = {}
+        self.log = []
+        self.peak_pages = 0
+
+    def limits(self):
+        return self.lim
+
+    def new_sequence(self):
+        s = self.free.pop()
+        self.len[s] = 0
+        return s
+
+    def end_sequence(self, slot):
+        assert slot in self.len, "slot freed twice"
+        del self.len[slot]
+        self.free.append(slot)
+
+    def step(self, items):
+        assert len({it.slot for it in items}) == len(items)
+        out = []
+        for it in items:
+            assert it.slot in self.len and len(it.tokens) >= 1
+            assert (self.len[it.slot] == 0) or len(it.tokens) == 1, "prompts only at the start"
+            self.len[it.slot] += len(it.tokens)
+            assert self.len[it.slot] <= self.lim.max_seq_len
+            for w in it.want:
+                out.append((it.slot, self.len[it.slot] - len(it.tokens) + w, tuple(it.tokens)))
+        pages = sum(-(-n // self.lim.page_size) for n in self.len.values())
+        assert pages <= self.lim.num_pages
+        self.peak_pages = max(self.peak_pages, pages)
+        self.log.append([(it.slot, len(it.tokens)) for it in items])
+        return out
+
+
+def scripted(script):
+    """chooser: request r's k-th generated token is script[r][k]."""
+    def choose(logits, requests, steps, histories):
+        assert len(logits) == len(requests)
+        return [script[r][s] for r, s in zip(requests, steps)]
+    return choose
+
+
+def test_plan_batches_by_slots_and_pages():
+    lim = Limits(max_batch=3, num_pages=6, page_size=4, max_seq_len=16)
+    assert plan_batches([3, 3, 3, 3], 1, lim) == [[0, 1, 2], [3]]
+    assert plan_batches([8, 8, 8], 4, lim) == [[0, 1], [2]]          # 3 pages each
+    with pytest.raises(RequestTooLong, match="longest sequence"):
+        plan_batches([17], 1, lim)
+    with pytest.raises(RequestTooLong, match="empty"):
+        plan_batches([0], 1, lim)
+    with pytest.raises(RequestTooLong, match="pages"):
+        plan_batches([12], 8, Limits(3, 3, 4, 32))
+
+
+def test_stop_tokens_end_sequences_early_and_are_kept():
+    be = FakeBackend()
+    script = {0: [7, 9, 8, 8, 8], 1: [4, 4, 4, 9, 8]}
+    res = generate(be, [[1, 2, 3], [1]], scripted(script), max_new_tokens=5, stop_ids=[9])
+    assert res.tokens == [[7, 9], [4, 4, 4, 9]]
+    assert res.finish == ["stop", "stop"]
+    # step log: prefill of both, then both, then only request 1 (slot 1) twice
+    assert be.log == [[(0, 3), (1, 1)], [(0, 1), (1, 1)], [(1, 1)], [(1, 1)]]
+    assert be.len == {} and sorted(be.free) == [0, 1]
+    assert res.decode_steps == 3 and res.decode_tokens == 4 and res.prefill_tokens == 4
+
+
+def test_max_new_tokens_and_no_step_after_the_last_token():
+    be = FakeBackend()
+    res = generate(be, [[1, 2]], scripted({0: [5, 6, 7, 8]}), max_new_tokens=3)
+    assert res.tokens == [[5, 6, 7]] and res.finish == ["length"]
+    assert len(be.log) == 3  # prefill + 2 decode steps; the third token is never fed back
+
+
+def test_context_limit():
+    be = FakeBackend(max_seq_len=6, num_pages=8)
+    res = generate(be, [[1, 2, 3, 4]], scripted({0: [5] * 10}), max_new_tokens=10)
+    # positions 0..5 hold 4 prompt + 2 generated tokens; the third generated token has no place
+    assert res.tokens == [[5, 5, 5]] and res.finish == ["context"]
+    assert be.len == {}
+
+
+def test_batches_run_one_after_another_and_reuse_slots():
+    be = FakeBackend(max_batch=2, num_pages=4, page_size=4, max_seq_len=8)
+    prompts = [[1] * 3, [2] * 2, [3] * 4, [4], [5] * 2]
+    script = {r: [10 + r] * 4 for r in range(5)}
+    seen = []
+    res = generate(be, prompts, scripted(script), max_new_tokens=2, on_token=lambda r, t: seen.append((r, t)))
+    assert res.batches == [[0, 1], [2, 3], [4]]
+    assert res.tokens == [[10 + r] * 2 for r in range(5)]
+    assert [n for _, n in be.log[0]] == [3, 2] and [n for _, n in be.log[2]] == [4, 1]
+    assert {s for s, _ in be.log[2]} == {0, 1} and len(be.log[4]) == 1   # the same two slots again
+    assert sorted(seen) == sorted((r, 10 + r) for r in range(5) for _ in range(2))
+    assert be.peak_pages <= 4 and be.len == {}
+
+
+def test_history_passed_to_the_chooser_includes_prompt_and_generated():
+    be = FakeBackend()
+    got = []
+
+    def choose(logits, requests, steps, histories):
+        got.append([list(h) for h in histories])
+        return [9 for _ in requests]
+
+    generate(be, [[1, 2], [3]], choose, max_new_tokens=2)
+    assert got == [[[1, 2], [3]], [[1, 2, 9], [3, 9]]]
+
+
+def test_slots_are_returned_when_a_step_raises():
+    class Boom(FakeBackend):
+        def step(self, items):
+            if len(self.log) == 1:
+                raise RuntimeError("boom")
+            return super().step(items)
+
+    be = Boom()
+    with pytest.raises(RuntimeError):
+        generate(be, [[1], [2]], scripted({0: [5] * 3, 1: [5] * 3}), max_new_tokens=3)
+    assert be.len == {} and sorted(be.free) == [0, 1]
+
+
+def test_zero_new_tokens():
+    be = FakeBackend()
+    res = generate(be, [[1]], scripted({0: []}), max_new_tokens=0)
+    assert res.tokens == [[]] and be.log == []

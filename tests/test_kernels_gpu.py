@@ -1,0 +1,373 @@
+"""Each CUDA kernel alone against its plain reference, at sizes other than the tiny models'
+(GPU).  Inputs of the bfloat16 cases are bfloat16 values, so the reference sees the same
+numbers and only the kernel's own rounding is left."""
+import math
+
+import numpy as np
+import plain_llama as plain
+import pytest
+import torch
+
+from inferllm_b200.kernels import ops
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def dev(x, dtype=None):
+    t = torch.as_tensor(x)
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda().contiguous()
+
+
+def f64(t):
+    return t.detach().double().cpu().numpy()
+
+
+def maxrel(got, ref):
+    got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    return float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+def err_word():
+    return torch.zeros(1, dtype=torch.int32, device="cuda")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("V,H", [(50, 24), (1000, 4096), (333, 1001)])
+def test_embedding(dtype, V, H):
+    g = torch.Generator().manual_seed(V)
+    table = torch.randn(V, H, generator=g).to(DT[dtype])
+    ids = torch.randint(0, V, (37,), generator=g, dtype=torch.int32)
+    err = err_word()
+    out = ops.embedding(dev(ids), dev(table), err)
+    assert out.dtype == torch.float32
+    assert np.array_equal(f64(out), plain.embed(ids.numpy(), f64(table)))
+    assert int(err.item()) == 0
+    bad = ids.clone()
+    bad[5] = V
+    out = ops.embedding(dev(bad), dev(table), err)
+    assert int(err.item()) == 1 and float(out[5].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype,wdtype", [("float32", "float32"), ("bfloat16", "bfloat16"),
+                                          ("bfloat16", "float32")])
+@pytest.mark.parametrize("T,H,eps", [(5, 64, 1e-5), (3, 4096, 1e-6), (17, 1000, 1e-3), (2, 11008, 1e-5)])
+def test_add_rmsnorm(dtype, wdtype, T, H, eps):
+    g = torch.Generator().manual_seed(H)
+    resid = torch.randn(T, H, generator=g) * 3
+    delta = (torch.randn(T, H, generator=g)).to(DT[dtype])
+    w = (1 + 0.1 * torch.randn(H, generator=g)).to(DT[wdtype])
+    tol = 1e-6 if dtype == "float32" else 2 ** -8
+    # plain norm
+    r = dev(resid)
+    y = ops.add_rmsnorm(r, None, dev(w), eps, DT[dtype])
+    assert maxrel(f64(y), plain.rms_norm(f64(resid), f64(w), eps)) <= tol
+    assert torch.equal(r.cpu(), resid)
+    # add + norm, stream updated
+    y = ops.add_rmsnorm(r, dev(delta), dev(w), eps, DT[dtype])
+    x = f64(resid) + f64(delta)
+    assert maxrel(f64(y), plain.rms_norm(x, f64(w), eps)) <= tol
+    assert maxrel(f64(r), x) <= 1e-7
+    # gathered rows, stream untouched
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32)
+    r2 = dev(resid)
+    y = ops.add_rmsnorm(r2, dev(delta), dev(w), eps, DT[dtype], rows=dev(rows), write_resid=False)
+    assert y.shape == (2, H)
+    assert maxrel(f64(y), plain.rms_norm(x[[T - 1, 0]], f64(w), eps)) <= tol
+    assert torch.equal(r2.cpu(), resid)
+    ops.residual_add(r2, dev(delta))
+    assert maxrel(f64(r2), x) <= 1e-7
+
+
+def test_rmsnorm_refuses_rows_wider_than_a_block_can_hold():
+    with pytest.raises(ops.KernelError, match="width"):
+        ops.add_rmsnorm(torch.zeros(1, 60000, device="cuda"), None, torch.ones(60000, device="cuda"),
+                        1e-5, torch.float32)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,I", [(1, 176), (9, 11008), (300, 100), (70000, 8)])
+def test_swiglu(dtype, T, I):
+    g = torch.Generator().manual_seed(I)
+    gu = (torch.randn(T, 2 * I, generator=g) * 2).to(DT[dtype])
+    out = ops.swiglu(dev(gu))
+    x = f64(gu)
+    ref = plain.silu(x[:, :I]) * x[:, I:]
+    assert maxrel(f64(out), ref) <= (1e-6 if dtype == "float32" else 2 ** -8)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (3, 70, 18), (64, 64, 16), (65, 129, 100), (200, 33, 7),
+                                   (8, 1000, 4096), (130, 50, 30)])
+def test_gemm_f32(M, N, K):
+    g = torch.Generator().manual_seed(M * N + K)
+    x, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
+    out = ops.gemm_f32(dev(x), dev(w))
+    assert maxrel(f64(out), plain.linear(f64(x), f64(w))) <= 1e-6 * math.sqrt(K)
+
+
+def test_gemm_f32_is_true_float32_and_row_invariant():
+    """Values that a reduced-precision product would lose, and the same bits for a row whatever
+    else is in the matrix."""
+    K = 512
+    x = torch.full((70, K), 1.0)
+    x[:, 0] = 1.0 + 2.0 ** -20        # lost by tf32 (10 bits) and by bfloat16 operands
+    w = torch.zeros(3, K)
+    w[:, 0] = 1.0
+    out = ops.gemm_f32(dev(x), dev(w)).cpu()
+    assert float(out[0, 0]) == 1.0 + 2.0 ** -20
+    g = torch.Generator().manual_seed(0)
+    x, w = torch.randn(133, 300, generator=g), torch.randn(77, 300, generator=g)
+    full = ops.gemm_f32(dev(x), dev(w)).cpu()
+    for r in (0, 64, 132):
+        one = ops.gemm_f32(dev(x[r:r + 1]), dev(w)).cpu()
+        assert torch.equal(one[0], full[r])
+
+
+@pytest.mark.parametrize("M,N,K", [(5, 96, 64), (2048, 300, 128), (1, 1000, 4096)])
+def test_linear_bf16(M, N, K):
+    g = torch.Generator().manual_seed(K)
+    x, w = torch.randn(M, K, generator=g).bfloat16(), torch.randn(N, K, generator=g).bfloat16()
+    ref = plain.linear(f64(x), f64(w))
+    out32 = ops.linear(dev(x), dev(w), out_dtype=torch.float32)
+    assert out32.dtype == torch.float32 and maxrel(f64(out32), ref) <= 1e-5
+    out = ops.linear(dev(x), dev(w))
+    assert out.dtype == torch.bfloat16 and maxrel(f64(out), ref) <= 2 ** -8
+
+
+# ---- rope + cache write, attention: a hand-made paged cache
+
+
+class Paged:
+    """Sequences of given lengths in a paged cache whose pages are dealt out in a shuffled
+    order; K and V of every position are known, so the plain reference can run on them."""
+
+    def __init__(self, lens, nkv, d, page, dtype, seed=0, spare_pages=3):
+        g = torch.Generator().manual_seed(seed)
+        self.lens, self.nkv, self.d, self.page = lens, nkv, d, page
+        self.width = max(-(-n // page) for n in lens) + 1
+        n_pages = sum(-(-n // page) for n in lens) + spare_pages
+        order = torch.randperm(n_pages, generator=g).tolist()
+        self.table = torch.full((len(lens), self.width), -1, dtype=torch.int32)
+        for b, n in enumerate(lens):
+            for lp in range(-(-n // page)):
+                self.table[b, lp] = order.pop()
+        self.k = [torch.randn(n, nkv, d, generator=g).to(dtype) for n in lens]
+        self.v = [torch.randn(n, nkv, d, generator=g).to(dtype) for n in lens]
+        # unused places hold NaN: a kernel that reads beyond a sequence's keys shows it
+        self.kc = torch.full((n_pages, nkv, page, d), float("nan"), dtype=dtype)
+        self.vc = torch.full((n_pages, nkv, page, d), float("nan"), dtype=dtype)
+        for b, n in enumerate(lens):
+            for p in range(n):
+                pg = int(self.table[b, p // page])
+                self.kc[pg, :, p % page] = self.k[b][p]
+                self.vc[pg, :, p % page] = self.v[b][p]
+
+
+def plain_attention_rows(q, k, v, pos, nh, nkv, scale, window):
+    """Plain attention of query rows at absolute positions `pos` over keys 0..len-1."""
+    s = plain.attention_scores(q, k, nh, nkv)
+    n_k = k.shape[0]
+    t = np.arange(n_k)[None, :]
+    hide = t > np.asarray(pos)[:, None]
+    if window:
+        hide |= t < np.asarray(pos)[:, None] - window + 1
+    s = np.where(hide[None], -np.inf, s * scale)
+    return plain.weighted_values(plain.softmax_rows(s), v, nh, nkv)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,d,page,window", [
+    (4, 4, 16, 8, None), (6, 2, 24, 16, None), (8, 1, 64, 64, None), (5, 5, 128, 32, None),
+    (3, 1, 256, 16, None), (4, 2, 40, 8, 13), (2, 2, 128, 64, 64)])
+def test_attention_generic(dtype, nh, nkv, d, page, window):
+    lens = [1, 37, 130, 64]
+    pc = Paged(lens, nkv, d, page, DT[dtype], seed=d)
+    g = torch.Generator().manual_seed(7)
+    # queries: all positions of sequence 1 (a prompt), the last of the others (decode), and
+    # a mid-sequence chunk of sequence 2
+    rows = [(1, p) for p in range(lens[1])] + [(0, 0), (2, 129), (3, 63)] + [(2, p) for p in range(60, 70)]
+    T = len(rows)
+    q = torch.randn(T, nh, d, generator=g).to(DT[dtype])
+    qkv = torch.cat([q.reshape(T, nh * d), torch.zeros(T, 2 * nkv * d, dtype=DT[dtype])], dim=1)
+    seq = torch.tensor([r[0] for r in rows], dtype=torch.int32)
+    pos = torch.tensor([r[1] for r in rows], dtype=torch.int32)
+    scale = 1.0 / math.sqrt(d)
+    out = ops.attention_generic(dev(qkv), dev(pc.kc), dev(pc.vc), dev(pc.table), dev(pos), dev(seq),
+                                nh, nkv, d, page, window, scale)
+    got = f64(out)
+    assert np.isfinite(got).all()
+    for b in range(len(lens)):
+        idx = [i for i, r in enumerate(rows) if r[0] == b]
+        ref = plain_attention_rows(f64(q[idx]), f64(pc.k[b]), f64(pc.v[b]), [rows[i][1] for i in idx],
+                                   nh, nkv, scale, window)
+        assert maxrel(got[idx], ref) <= (2e-6 if dtype == "float32" else 2 ** -7)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_finds_one_far_key_among_hundreds(dtype):
+    """One key far back (first page) matches the query strongly: the output must be its value.
+    A kernel that drops, misplaces or mis-masks far keys fails here although random data would
+    average the fault away."""
+    nh = nkv = 2
+    d, page, n = 64, 16, 900
+    pc = Paged([n], nkv, d, page, DT[dtype], seed=1)
+    for target in (3, 15, 16, 447, 899):
+        q = torch.zeros(1, nh, d)
+        kc, vc = pc.kc.clone(), pc.vc.clone()
+        key = torch.randn(d, generator=torch.Generator().manual_seed(target))
+        key = (key / key.norm() * 12).to(DT[dtype])
+        pg = int(pc.table[0, target // page])
+        kc[pg, :, target % page] = key
+        q[0, :] = key.float() * 2
+        qkv = torch.cat([q.reshape(1, nh * d), torch.zeros(1, 2 * nkv * d)], dim=1).to(DT[dtype])
+        out = ops.attention_generic(dev(qkv), dev(kc), dev(vc), dev(pc.table),
+                                    dev(torch.tensor([n - 1], dtype=torch.int32)),
+                                    dev(torch.zeros(1, dtype=torch.int32)), nh, nkv, d, page, None, 1.0)
+        want = f64(pc.v[0][target]).reshape(-1)
+        assert maxrel(f64(out).reshape(-1), want) <= 1e-2, f"key {target} was not found"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_window_edge(dtype):
+    """The oldest key inside the window counts and the one before it does not."""
+    nh = nkv = 1
+    d, page, n, window = 32, 8, 100, 24
+    pc = Paged([n], nkv, d, page, DT[dtype], seed=2)
+    p = n - 1
+    key = torch.ones(d) * 3
+    for target, inside in ((p - window + 1, True), (p - window, False)):
+        kc = pc.kc.clone()
+        kc[int(pc.table[0, target // page]), 0, target % page] = key.to(DT[dtype])
+        qkv = torch.cat([key * 2, torch.zeros(2 * d)]).reshape(1, -1).to(DT[dtype])
+        out = f64(ops.attention_generic(dev(qkv), dev(kc), dev(pc.vc), dev(pc.table),
+                                        dev(torch.tensor([p], dtype=torch.int32)),
+                                        dev(torch.zeros(1, dtype=torch.int32)), 1, 1, d, page, window, 1.0))
+        hit = maxrel(out.reshape(-1), f64(pc.v[0][target]).reshape(-1)) <= 1e-2
+        assert hit == inside
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,d,rot,page,theta", [(4, 4, 16, 16, 8, 1e4), (6, 2, 24, 24, 16, 5e5),
+                                                     (3, 1, 128, 64, 64, 1e6), (2, 2, 64, 0, 32, 1e4)])
+def test_rope_and_cache_write(dtype, nh, nkv, d, rot, page, theta):
+    from inferllm_b200.config import PartSpec
+    from inferllm_b200.parts import Runtime, build_part
+    lens = [70, 5]
+    starts = [64, 0]      # sequence 0 appends positions 64..69, sequence 1 is a new prompt
+    pc = Paged(lens, nkv, d, page, DT[dtype], seed=3)
+    rows = [(0, p) for p in range(starts[0], lens[0])] + [(1, p) for p in range(lens[1])]
+    T = len(rows)
+    g = torch.Generator().manual_seed(11)
+    qkv = torch.randn(T, (nh + 2 * nkv) * d, generator=g).to(DT[dtype])
+    seq = torch.tensor([r[0] for r in rows], dtype=torch.int32)
+    pos = torch.tensor([r[1] for r in rows], dtype=torch.int32)
+    table = None
+    if rot:
+        rt = Runtime(torch.device("cuda"), DT[dtype])
+        part = build_part("position", PartSpec("rope_half", dict(head_dim=d, rot_dim=rot, theta=theta,
+                                                                 max_positions=128)), rt)
+        part.prepare()
+        table = part.table
+    kc, vc, x = dev(pc.kc), dev(pc.vc), dev(qkv)
+    err = err_word()
+    ops.rope_kv_write(x, table, rot, dev(pos), dev(seq), dev(pc.table), kc, vc, nh, nkv, d, page, True, err)
+    assert int(err.item()) == 0
+    src = f64(qkv).reshape(T, nh + 2 * nkv, d)
+    want = plain.rope_rotate_half(src[:, :nh + nkv], pos.numpy(), theta, rot) if rot else src[:, :nh + nkv]
+    tol = 1e-6 if dtype == "float32" else 2 ** -8
+    got = f64(x).reshape(T, nh + 2 * nkv, d)
+    assert maxrel(got[:, :nh], want[:, :nh]) <= tol
+    assert np.array_equal(got[:, nh:], src[:, nh:])          # K and V columns are left alone
+    kc, vc = f64(kc), f64(vc)
+    for i, (b, p) in enumerate(rows):
+        pg = int(pc.table[b, p // page])
+        assert maxrel(kc[pg, :, p % page], want[i, nh:]) <= tol
+        assert np.array_equal(vc[pg, :, p % page], src[i, nh + nkv:])
+    # places that were not written keep what they held
+    old_k = f64(pc.kc)
+    keep = np.ones(old_k.shape[:3:2], bool)  # [pages, page]
+    for b, p in rows:
+        keep[int(pc.table[b, p // page]), p % page] = False
+    a, b_ = kc.transpose(0, 2, 1, 3)[keep], old_k.transpose(0, 2, 1, 3)[keep]
+    assert np.array_equal(np.isnan(a), np.isnan(b_)) and np.array_equal(a[~np.isnan(a)], b_[~np.isnan(b_)])
+    # a token whose page is missing raises the error word and writes nothing
+    bad = pc.table.clone()
+    bad[1, 0] = -1
+    ops.rope_kv_write(dev(qkv), table, rot, dev(pos), dev(seq), dev(bad), dev(pc.kc), dev(pc.vc),
+                      nh, nkv, d, page, True, err)
+    assert int(err.item()) == 2
+
+
+def test_rope_angles_at_far_positions_match_float64():
+    """theta^(-2j/d) * p for p in the thousands: a table computed in float32 arithmetic would be
+    off by 1e-4 and more; the kernel's table is float64 rounded once."""
+    from inferllm_b200.config import PartSpec
+    from inferllm_b200.parts import Runtime, build_part
+    d = 128
+    part = build_part("position", PartSpec("rope_half", dict(head_dim=d, theta=1e4, max_positions=8192)),
+                      Runtime(torch.device("cuda"), torch.float32))
+    part.prepare()
+    pos = np.array([8191, 4097, 1])
+    x = np.zeros((3, 1, d))
+    x[:, :, :d // 2] = 1.0
+    ref = plain.rope_rotate_half(x, pos, 1e4)
+    qkv = torch.zeros(3, 3 * d)
+    qkv[:, :d // 2] = 1.0
+    kc = torch.zeros(130, 1, 64, d, device="cuda")
+    tab = torch.arange(129, dtype=torch.int32).reshape(1, 129).cuda()
+    t = dev(qkv)
+    ops.rope_kv_write(t, part.table, d, dev(torch.tensor(pos, dtype=torch.int32)),
+                      dev(torch.zeros(3, dtype=torch.int32)), tab, kc, kc.clone(), 1, 1, d, 64, True, err_word())
+    assert np.abs(f64(t)[:, :d] - ref[:, 0]).max() <= 2e-7
+
+
+# ---- sampling
+
+
+@pytest.mark.parametrize("B,V", [(1, 10), (7, 32000), (3, 128256), (64, 513)])
+def test_argmax(B, V):
+    g = torch.Generator().manual_seed(V)
+    lg = torch.randn(B, V, generator=g)
+    lg[0, V // 2] = lg[0, V - 1] = 50.0      # equal maxima: the lowest id wins
+    out = ops.argmax(dev(lg)).cpu()
+    want = lg.argmax(-1)
+    want[0] = V // 2
+    assert out.tolist() == want.tolist()
+
+
+@pytest.mark.parametrize("temp,top_k,top_p,pen", [(0.8, 0, 1.0, 1.0), (1.0, 5, 1.0, 1.0), (0.7, 0, 0.9, 1.0),
+                                                  (1.3, 40, 0.95, 1.3), (0.5, 3, 0.5, 1.1)])
+def test_sample_distribution_matches_the_reference_sampler(temp, top_k, top_p, pen):
+    """Draw with a fine grid of uniform numbers and compare the frequencies of the chosen ids
+    with the probabilities of the reference's algorithm."""
+    V, N = 97, 20000
+    g = torch.Generator().manual_seed(5)
+    logits = (torch.randn(V, generator=g) * 2.5)
+    last = [3, 17, 17, 96, -1, 40]
+    ids, probs = plain.sample_distribution(logits.numpy(), [t for t in last if t >= 0], pen, top_k, top_p, temp)
+    want = np.zeros(V)
+    want[ids] = probs
+    u = (torch.arange(N, dtype=torch.float32) + 0.5) / N
+    lg = logits.repeat(N, 1)
+    lt = torch.tensor(last, dtype=torch.int32).repeat(N, 1)
+    out = ops.sample(dev(lg), dev(u), temp, top_k, top_p, pen, dev(lt)).cpu().numpy()
+    freq = np.bincount(out, minlength=V) / N
+    assert set(np.nonzero(freq)[0]) <= set(ids.tolist()), "an id outside the kept set was drawn"
+    assert np.abs(freq - want).max() <= 2.0 / N + 1e-4
+    # the same uniform number gives the same id whatever else is in the batch
+    one = ops.sample(dev(lg[:1]), dev(u[1234:1235]), temp, top_k, top_p, pen, dev(lt[:1])).cpu().numpy()
+    assert one[0] == out[1234]
+
+
+def test_sample_large_vocabulary_and_greedy_limit():
+    V = 128256
+    g = torch.Generator().manual_seed(9)
+    lg = torch.randn(4, V, generator=g)
+    lg[2, 77777] = 30.0
+    u = torch.tensor([0.1, 0.5, 0.9, 0.999])
+    out = ops.sample(dev(lg), dev(u), 1.0, 1, 1.0, 1.0, None).cpu()
+    assert out.tolist() == lg.argmax(-1).tolist()     # top_k = 1 is greedy
+    out = ops.sample(dev(lg), dev(u), 0.05, 0, 0.3, 1.0, None).cpu()
+    assert out[2] == 77777
