@@ -1,0 +1,264 @@
+#!/usr/bin/env python3
+"""Benchmark of inferllm_b200 on one B200: decode tokens per second of a LLaMA-2-7B-sized
+model with random weights (the headline: batch 8 at the end of a 4096-token context), the same
+through the Python entry point with host tokens in and out, a 2,048-token prefill, and decode
+at batch 1 and 64.  Prints ONE JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch.  Timing is by CUDA events on the launching
+stream after the warm-up steps; every step reads all weights (13 GB, far larger than the L2),
+so nothing is served from cache between steps.  The reference (MegEngine/InferLLM) publishes
+only CPU int4 numbers for this architecture (docs/profile.md: 3.2-12.7 tok/s), has no GPU
+number, no batch above 1 and cannot be pip-installed, so `vs_baseline` is null and
+`--impl reference` reports why it is unavailable.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: LLaMA-2-7B size, benchmark context 4096
+CONFIG_7B = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidden_layers=32,
+                 num_attention_heads=32, num_key_value_heads=32, head_dim=128,
+                 intermediate_size=11008, vocab_size=32000, rope_theta=10000.0, rms_norm_eps=1e-5,
+                 max_position_embeddings=4096, tie_word_embeddings=False)
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(d.get(k), (int, float)):
+                    out[k] = float(d[k])
+            return out, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device=0):
+        self.samples, self.proc, self.device = [], None, device
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6 and parts[0].isdigit():
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        mhz = sorted(int(s[0]) for s in self.samples)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(self.samples[0][1]), "reasons": reasons,
+                "samples": len(mhz)}
+
+
+def model_figures(cfg, n_layers):
+    """Bytes and flops of one step, from the configuration."""
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = (nh + 2 * nkv) * d * H + H * nh * d + 3 * H * I          # matrix elements
+    matrix = n_layers * per_layer + V * H                                # + the output matrix
+    norms = (2 * n_layers + 1) * H
+    weight_bytes = 2 * (matrix + norms)
+    kv_bytes_per_token = 2 * nkv * d * 2 * n_layers
+    return {"matrix_elems": matrix, "weight_bytes": weight_bytes, "kv_bytes_per_token": kv_bytes_per_token,
+            "layer_matrix_elems": per_layer}
+
+
+def prefill_flops(cfg, n_layers, T, fig):
+    nh, d = cfg["num_attention_heads"], cfg["head_dim"]
+    linear = 2 * T * (n_layers * fig["layer_matrix_elems"]) + 2 * 1 * cfg["vocab_size"] * cfg["hidden_size"]
+    attn = n_layers * nh * 4 * d * (T * (T + 1) // 2)                     # QK^T and PV over the causal half
+    return linear + attn
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args()
+
+    if args.gpus != 1:
+        print(f"bench.py: inferllm_b200 is a single-GPU library; --gpus {args.gpus} is not supported (N=1 only)")
+        return 2
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "MegEngine/InferLLM is a CMake C++ project, not a Python package: pip reports "
+                          "'neither setup.py nor pyproject.toml found'; it also has no batch > 1 and no bf16 path"}))
+        return 0
+    K, W = args.steps, max(3, args.warmup)
+
+    import torch
+
+    from inferllm_b200 import Model, ModelConfig, StepItem, config_from_dict
+    from inferllm_b200.kernels import ops
+
+    cfgd = dict(CONFIG_7B)
+    full_layers = cfgd["num_hidden_layers"]
+    if args.layers:
+        cfgd["num_hidden_layers"] = args.layers
+    L = cfgd["num_hidden_layers"]
+    cfg = config_from_dict(cfgd)
+    fig = model_figures(cfgd, L)
+    pk, pk_src = peaks()
+    B = args.batch
+
+    # one engine for every scenario: cache for the batch at full context, or 64 short sequences
+    decode_room = K + W + 8
+    max_tokens = max(B * CONTEXT, 64 * (-(-(512 + decode_room) // 64) * 64), PREFILL_TOKENS) + 64
+    model = Model(ModelConfig(compt_type="bfloat16", nr_ctx=CONTEXT, max_tokens=max_tokens, max_batch=max(B, 64)))
+    model.load_random(cfg, seed=0)
+    model.init(top_k=0, top_p=1.0, temp=0.0, repeat_penalty=1.0, repeat_last_n=0, seed=0, end_token=-1)
+    eng = model.engine
+    g = torch.Generator().manual_seed(0)
+
+    def rand_ids(n):
+        return torch.randint(0, cfgd["vocab_size"], (n,), generator=g).tolist()
+
+    def timed(fn, n):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    # ---- prefill of one 2,048-token prompt
+    prompt = rand_ids(PREFILL_TOKENS)
+
+    def prefill_once():
+        s = eng.new_sequence()
+        eng.step([StepItem(s, prompt, [PREFILL_TOKENS - 1])])
+        eng.end_sequence(s)
+
+    for _ in range(3):
+        prefill_once()
+    pf_ms = timed(prefill_once, 3)
+    pf_flops = prefill_flops(cfgd, L, PREFILL_TOKENS, fig)
+    prefill = {"value": round(PREFILL_TOKENS / pf_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
+               "frac": round(pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               "tflops": round(pf_flops / (pf_ms * 1e-3) / 1e12, 1)}
+
+    # ---- decode: `batch` sequences, timed steps end at position `ctx_end`
+    def decode_run(batch, ctx_end, steps, warm):
+        start = ctx_end - steps - warm
+        slots = [eng.new_sequence() for _ in range(batch)]
+        per_step = max(1, 8192 // start)                  # prompts go in steps of about 8k tokens
+        for i in range(0, batch, per_step):
+            eng.step([StepItem(s, rand_ids(start), []) for s in slots[i:i + per_step]])
+        toks = [[t] for t in rand_ids(batch)]
+
+        def one():
+            eng.step([StepItem(s, t, [0]) for s, t in zip(slots, toks)])
+
+        for _ in range(warm):
+            one()
+        before = ops.launch_count()
+        with ClockSampler() as cs:
+            ms = timed(one, steps)
+        launches = ops.launch_count() - before
+        for s in slots:
+            eng.end_sequence(s)
+        return ms, launches, cs.summary()
+
+    ms, launches, clocks = decode_run(B, CONTEXT, K, W)
+    value = B / ms * 1e3
+    ctx_mid = CONTEXT - K // 2
+    step_bytes = fig["weight_bytes"] + B * ctx_mid * fig["kv_bytes_per_token"]
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk_src,
+                "bytes_per_step": step_bytes}
+
+    # ---- the same through the Python entry point: host token ids in, host token ids out
+    plen = CONTEXT - K - 1
+    model.generate([rand_ids(64) for _ in range(B)], max_new_tokens=4, stop_ids=[])      # warm-up
+    res = model.generate([rand_ids(plen) for _ in range(B)], max_new_tokens=K + 1, stop_ids=[])
+    e2e_val = res.decode_tokens / res.decode_s
+    h2d = eng.last_upload_bytes          # token ids, positions, slots and page table of the last step
+    e2e = {"value": round(e2e_val, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B,
+           "steps": res.decode_steps}
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            pms, _, _ = decode_run(b, 512 + K + W, K, W)
+            points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+        pms, _, _ = decode_run(B, 512 + K + W, K, W)
+        points[f"decode_b{B}_ctx512"] = round(B / pms * 1e3, 1)
+        points["ctx_of_b1_b64"] = 512
+
+    line = {
+        "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048-token prompt",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: uniform-random token ids, random-init weights N(0, 0.02)",
+        "impl": "ours",
+        "config": {"model": "LLaMA-2-7B size", "global_batch": B, "seq_len": CONTEXT, "parallelism": "none (1 GPU)",
+                   "layers": L, "layers_of_config": full_layers, "hidden": cfgd["hidden_size"],
+                   "heads": cfgd["num_attention_heads"], "kv_heads": cfgd["num_key_value_heads"],
+                   "head_dim": cfgd["head_dim"], "intermediate": cfgd["intermediate_size"],
+                   "vocab": cfgd["vocab_size"], "context_len": CONTEXT,
+                   "decode_positions": f"{CONTEXT - K}..{CONTEXT}", "prefill_tokens": PREFILL_TOKENS,
+                   "l2": "inputs larger than L2 (13 GB of weights read per step)", "page_size": 64,
+                   "peaks": pk_src},
+        "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "prefill": prefill, "roofline": roofline,
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -185,6 +185,7 @@ class Engine:
             host[o:o + p.size] = torch.from_numpy(p)
         buf = torch.empty(total, dtype=torch.int32, device=self.rt.device)
         buf.copy_(host[:total], non_blocking=True)
+        self.last_upload_bytes = 4 * total
         self._staging_busy = torch.cuda.Event()
         self._staging_busy.record()
         return buf

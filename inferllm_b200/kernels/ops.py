@@ -25,7 +25,17 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernels of this package have been launched (library products not counted)."""
+    return _launches
+
+
 def _check(code, what):
+    global _launches
+    _launches += 1
     if code != 0:
         if code == 10001:
             raise KernelError(f"{what}: the kernel refused its arguments")
