@@ -125,6 +125,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--only", choices=["decode", "prefill"], help="run one scenario (for profiling); "
+                    "prints a short JSON line of that scenario only")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="position at which the timed decode steps end")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -174,22 +177,6 @@ def main():
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / n
 
-    # ---- prefill of one 2,048-token prompt
-    prompt = rand_ids(PREFILL_TOKENS)
-
-    def prefill_once():
-        s = eng.new_sequence()
-        eng.step([StepItem(s, prompt, [PREFILL_TOKENS - 1])])
-        eng.end_sequence(s)
-
-    for _ in range(3):
-        prefill_once()
-    pf_ms = timed(prefill_once, 3)
-    pf_flops = prefill_flops(cfgd, L, PREFILL_TOKENS, fig)
-    prefill = {"value": round(PREFILL_TOKENS / pf_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
-               "frac": round(pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
-               "tflops": round(pf_flops / (pf_ms * 1e-3) / 1e12, 1)}
-
     # ---- decode: `batch` sequences, timed steps end at position `ctx_end`
     def decode_run(batch, ctx_end, steps, warm):
         start = ctx_end - steps - warm
@@ -211,6 +198,31 @@ def main():
         for s in slots:
             eng.end_sequence(s)
         return ms, launches, cs.summary()
+
+    if args.only == "decode":
+        ms, launches, clocks = decode_run(B, args.context, K, W)
+        print(json.dumps({"only": "decode", "batch": B, "layers": L, "context": args.context,
+                          "ms_per_step": round(ms, 4), "gpu_launches": launches}))
+        return 0
+
+    # ---- prefill of one 2,048-token prompt
+    prompt = rand_ids(PREFILL_TOKENS)
+
+    def prefill_once():
+        s = eng.new_sequence()
+        eng.step([StepItem(s, prompt, [PREFILL_TOKENS - 1])])
+        eng.end_sequence(s)
+
+    for _ in range(3):
+        prefill_once()
+    pf_ms = timed(prefill_once, 3)
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "layers": L, "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3)}))
+        return 0
+    pf_flops = prefill_flops(cfgd, L, PREFILL_TOKENS, fig)
+    prefill = {"value": round(PREFILL_TOKENS / pf_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
+               "frac": round(pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               "tflops": round(pf_flops / (pf_ms * 1e-3) / 1e12, 1)}
 
     ms, launches, clocks = decode_run(B, CONTEXT, K, W)
     value = B / ms * 1e3

@@ -1,0 +1,211 @@
+// Attention of single tokens over long paged caches, bfloat16, bound by reading K and V once.
+//
+// One decode step must read every cached key and value of every live sequence; nothing else of
+// the attention costs anything.  So the work is cut for bandwidth: a block owns one
+// (token, kv head, chunk of 256 keys) and handles all query heads of that kv head together, so a
+// key or value is fetched once however many query heads share it (the reference's only grouped
+// attention loops over the query heads and re-reads K and V for each,
+// src/kern/gpu/kernel_gpu.cu:688-756).  Inside a block every key row is read by D/8 neighbouring
+// lanes with one 16-byte load each (fully coalesced), four keys per lane group in flight, and
+// each lane group keeps a running maximum, sum and weighted value sum of its own (scores and
+// softmax in float32; formulas src/kern/naive/naive.cpp:606-632, :531-553, :209-240, :664-691).
+// Partial results go to a scratch buffer [token, head, chunk] and a second kernel merges the
+// chunks of a token in ascending order.  Which keys fall into which chunk and lane group depends
+// only on the token's own position, so the result does not depend on the rest of the batch.
+// The grid covers the chunks of the longest possible sequence; blocks beyond a token's own
+// length return at once, which keeps the launch identical from step to step (CUDA graphs).
+#include <math.h>
+
+#include "common.cuh"
+
+#define AD_THREADS 128
+#define AD_CHUNK 256   // keys per block
+#define AD_U 4         // keys per lane group and iteration
+
+template <int D, int G>
+__global__ void __launch_bounds__(AD_THREADS)
+attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kc,
+                        const bf16* __restrict__ vc, const int* __restrict__ block_table, int max_pages,
+                        const int* __restrict__ token_pos, const int* __restrict__ token_seq,
+                        float* __restrict__ part_acc, float* __restrict__ part_ml, int n_chunks, int nh,
+                        int nkv, int page_size, int window, float scale_log2e) {
+    constexpr int LPK = D / 8;                 // lanes per key
+    constexpr int GROUPS = AD_THREADS / LPK;   // independent softmax streams in the block
+    const int chunk = blockIdx.x, hk = blockIdx.y, t = blockIdx.z;
+    const int p = token_pos[t];
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int c0 = chunk * AD_CHUNK;
+    if (c0 > p || c0 + AD_CHUNK <= lo) return;
+    const int first = c0 > lo ? c0 : lo;                       // first key of this block
+    const int last = (c0 + AD_CHUNK - 1 < p) ? c0 + AD_CHUNK - 1 : p;  // last key, inclusive
+
+    const int tid = threadIdx.x;
+    const int grp = tid / LPK, sub = tid % LPK;
+    const int* bt = block_table + (size_t)token_seq[t] * max_pages;
+
+    float qr[G][8];
+#pragma unroll
+    for (int g = 0; g < G; g++) load8(q + (size_t)t * q_stride + (size_t)(hk * G + g) * D + sub * 8, qr[g]);
+
+    float m[G], l[G], acc[G][8];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[g][i] = 0.f;
+    }
+
+    // lane group `grp` takes keys base + grp*AD_U + u of every stretch of GROUPS*AD_U keys
+    const int aligned = first - (first % AD_U);   // AD_U keys never straddle a page (page_size % AD_U == 0)
+    // (the trip count is the same for every lane of a warp: the shuffles below need all of them)
+    for (int base0 = aligned; base0 <= last; base0 += GROUPS * AD_U) {
+        const int base = base0 + grp * AD_U;
+        const int page = base <= last ? bt[base / page_size] : 0;
+        const size_t row0 = (((size_t)page * nkv + hk) * page_size + (base % page_size)) * D + sub * 8;
+        float kf[AD_U][8], vf[AD_U][8];
+        bool ok[AD_U];
+#pragma unroll
+        for (int u = 0; u < AD_U; u++) {
+            ok[u] = (base + u >= first) && (base + u <= last);
+            if (ok[u]) {
+                load8(kc + row0 + (size_t)u * D, kf[u]);
+                load8(vc + row0 + (size_t)u * D, vf[u]);
+            }
+        }
+        float s[G][AD_U];
+#pragma unroll
+        for (int g = 0; g < G; g++)
+#pragma unroll
+            for (int u = 0; u < AD_U; u++) {
+                float d = 0.f;
+                if (ok[u]) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) d = fmaf(qr[g][i], kf[u][i], d);
+                }
+#pragma unroll
+                for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                s[g][u] = ok[u] ? d * scale_log2e : -INFINITY;
+            }
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            float mn = m[g];
+#pragma unroll
+            for (int u = 0; u < AD_U; u++) mn = fmaxf(mn, s[g][u]);
+            if (mn == -INFINITY) continue;   // no valid key in this stretch for this group
+            const float corr = exp2f(m[g] - mn);  // m = -inf gives 0
+            float pe[AD_U], ps = 0.f;
+#pragma unroll
+            for (int u = 0; u < AD_U; u++) {
+                pe[u] = exp2f(s[g][u] - mn);
+                ps += pe[u];
+            }
+            l[g] = l[g] * corr + ps;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                float a = acc[g][i] * corr;
+#pragma unroll
+                for (int u = 0; u < AD_U; u++)
+                    if (ok[u]) a = fmaf(pe[u], vf[u][i], a);
+                acc[g][i] = a;
+            }
+            m[g] = mn;
+        }
+    }
+
+    // merge the lane groups of the block, in ascending order of group, through shared memory
+    __shared__ float sm_m[GROUPS][G], sm_l[GROUPS][G];
+    __shared__ float sm_acc[GROUPS][G][D];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        if (sub == 0) {
+            sm_m[grp][g] = m[g];
+            sm_l[grp][g] = l[g];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) sm_acc[grp][g][sub * 8 + i] = acc[g][i];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * D; idx += AD_THREADS) {
+        const int g = idx / D, c = idx - g * D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < GROUPS; r++) M = fmaxf(M, sm_m[r][g]);
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int r = 0; r < GROUPS; r++) {
+            const float w = (sm_m[r][g] == -INFINITY) ? 0.f : exp2f(sm_m[r][g] - M);
+            num += sm_acc[r][g][c] * w;
+            den += sm_l[r][g] * w;
+        }
+        const size_t o = ((size_t)t * nh + hk * G + g) * n_chunks + chunk;
+        part_acc[o * D + c] = num;
+        if (c == 0) {
+            part_ml[o * 2] = M;
+            part_ml[o * 2 + 1] = den;
+        }
+    }
+}
+
+template <int D>
+__global__ void attention_decode_merge_kernel(const float* __restrict__ part_acc,
+                                              const float* __restrict__ part_ml,
+                                              const int* __restrict__ token_pos, bf16* __restrict__ out,
+                                              int n_chunks, int nh, int window) {
+    const int h = blockIdx.x, t = blockIdx.y, c = threadIdx.x;
+    const int p = token_pos[t];
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int cfirst = lo / AD_CHUNK, clast = p / AD_CHUNK;
+    const size_t o = ((size_t)t * nh + h) * n_chunks;
+    float M = -INFINITY;
+    for (int ch = cfirst; ch <= clast; ch++) M = fmaxf(M, part_ml[(o + ch) * 2]);
+    float num = 0.f, den = 0.f;
+    for (int ch = cfirst; ch <= clast; ch++) {
+        const float w = exp2f(part_ml[(o + ch) * 2] - M);
+        den += part_ml[(o + ch) * 2 + 1] * w;
+        num += part_acc[(o + ch) * D + c] * w;
+    }
+    out[((size_t)t * nh + h) * D + c] = __float2bfloat16_rn(num / den);
+}
+
+template <int D, int G>
+static int launch(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table,
+                  int max_pages, const int* token_pos, const int* token_seq, float* part_acc,
+                  float* part_ml, void* out, int T, int nh, int nkv, int page_size, int window,
+                  float scale, int n_chunks, cudaStream_t s) {
+    dim3 grid(n_chunks, nkv, T);
+    attention_decode_kernel<D, G><<<grid, AD_THREADS, 0, s>>>(
+        (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, block_table, max_pages, token_pos,
+        token_seq, part_acc, part_ml, n_chunks, nh, nkv, page_size, window, scale * 1.4426950408889634f);
+    attention_decode_merge_kernel<D><<<dim3(nh, T), D, 0, s>>>(part_acc, part_ml, token_pos, (bf16*)out,
+                                                             n_chunks, nh, window);
+    return illm_launch_status();
+}
+
+// Scratch: part_acc float [T, nh, n_chunks, D], part_ml float [T, nh, n_chunks, 2], with
+// n_chunks = ceil(max_len / 256) for the longest sequence the launch may meet.
+extern "C" int illm_attention_decode(const void* q, int q_stride, const void* kc, const void* vc,
+                                     const int* block_table, int max_pages, const int* token_pos,
+                                     const int* token_seq, float* part_acc, float* part_ml, void* out,
+                                     int T, int nh, int nkv, int d, int page_size, int window,
+                                     float scale, int n_chunks, void* stream) {
+    if (T <= 0) return 0;
+    if (nkv <= 0 || nh % nkv || page_size % AD_U || T > 65535 || nkv > 65535) return ILLM_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int g = nh / nkv;
+#define AD_CASE(DD, GG)                                                                            \
+    if (d == DD && g == GG)                                                                        \
+        return launch<DD, GG>(q, q_stride, kc, vc, block_table, max_pages, token_pos, token_seq,  \
+                              part_acc, part_ml, out, T, nh, nkv, page_size, window, scale, n_chunks, s);
+    AD_CASE(128, 1) AD_CASE(128, 2) AD_CASE(128, 4) AD_CASE(128, 8)
+    AD_CASE(64, 1) AD_CASE(64, 2) AD_CASE(64, 3) AD_CASE(64, 4) AD_CASE(64, 8)
+#undef AD_CASE
+    return ILLM_ERR_BAD_ARG;
+}
+
+extern "C" int illm_attention_decode_supported(int d, int g, int page_size) {
+    if (page_size % AD_U) return 0;
+    if (d == 128) return g == 1 || g == 2 || g == 4 || g == 8;
+    if (d == 64) return g == 1 || g == 2 || g == 3 || g == 4 || g == 8;
+    return 0;
+}

@@ -19,6 +19,7 @@ import numpy as np
 import torch
 
 from ..cache import CacheError, SequenceCache
+from ..kernels import ops
 from ..parts.base import Runtime
 from ..registry import config_from_folder, get_architecture
 from ..weights import init_random_weights, load_model_weights
@@ -39,6 +40,7 @@ class EngineOptions:
     max_seq_len: Optional[int] = None   # longest sequence; default the model's max positions
     max_batch: Optional[int] = None     # slots; default max_tokens / page_size
     page_size: int = 64
+    cuda_graphs: bool = True       # replay one-token-per-sequence steps from captured CUDA graphs
 
 
 @dataclass
@@ -64,8 +66,10 @@ class StepContext:
     slots, seq_lens, cu_q : int32 [B], [B], [B+1]   slot, length after the step, token offsets
     """
 
-    def __init__(self, engine, plan, ids_host, want_rows_host):
-        cache, dev = engine.cache, engine.rt.device
+    def __init__(self, engine, plan, ids_host, want_rows_host, into=None):
+        """`into`: a device buffer of an earlier step of the same shape to fill again (the
+        static input of a captured graph); None uploads into a fresh buffer."""
+        cache = engine.cache
         B = len(plan.slots)
         q = np.asarray(plan.q_lens, dtype=np.int64)
         past = np.asarray(plan.past, dtype=np.int64)
@@ -82,7 +86,8 @@ class StepContext:
         for p in parts:
             offs.append(total)
             total += (p.size + 3) // 4 * 4  # keep every array 16-byte aligned
-        buf = engine._upload(parts, offs, total)
+        buf = engine._upload(parts, offs, total, into)
+        self.buffer = buf
 
         def view(i):
             return buf[offs[i]:offs[i] + parts[i].size]
@@ -95,6 +100,7 @@ class StepContext:
         self.max_q = int(q.max())
         self.max_len = int((past + q).max())
         self.is_decode = self.max_q == 1
+        self.max_seq_len = cache.max_seq_len
         self.err = engine.err
         self._cache = cache
 
@@ -129,6 +135,8 @@ class Engine:
         self.err = torch.zeros(1, dtype=torch.int32, device=dev)
         self._stage = None
         self._staging_busy = None
+        self._graphs = {}
+        self._graph_pool = None
         self.loaded = False
 
     def _make_runtime(self, options: EngineOptions) -> Runtime:
@@ -174,7 +182,7 @@ class Engine:
 
     # ---- the step
 
-    def _upload(self, parts, offs, total: int) -> torch.Tensor:
+    def _upload(self, parts, offs, total: int, into=None) -> torch.Tensor:
         """One pinned staging buffer, one asynchronous copy for all of a step's index arrays."""
         if self._staging_busy is not None:
             self._staging_busy.synchronize()  # the previous step's copy has left the buffer
@@ -183,7 +191,7 @@ class Engine:
         host = self._stage
         for o, p in zip(offs, parts):
             host[o:o + p.size] = torch.from_numpy(p)
-        buf = torch.empty(total, dtype=torch.int32, device=self.rt.device)
+        buf = into if into is not None else torch.empty(total, dtype=torch.int32, device=self.rt.device)
         buf.copy_(host[:total], non_blocking=True)
         self.last_upload_bytes = 4 * total
         self._staging_busy = torch.cuda.Event()
@@ -213,10 +221,43 @@ class Engine:
             ids.extend(int(t) for t in it.tokens)
             off += n
         plan = self.cache.plan_step([it.slot for it in items], [len(it.tokens) for it in items])
-        ctx = StepContext(self, plan, ids, want_rows)
-        logits = self.model.forward(ctx)
+        if self.options.cuda_graphs and len(ids) == len(items) and self.model.graph_safe():
+            logits = self._decode_step_graphed(plan, ids, want_rows)
+        else:
+            logits = self.model.forward(StepContext(self, plan, ids, want_rows))
         self.cache.commit_step(plan)
         return logits
+
+    def _decode_step_graphed(self, plan, ids, want_rows) -> torch.Tensor:
+        """One token per sequence: the launches of such a step are the same every time (all that
+        changes lies in device memory), so the step is captured in a CUDA graph the second time
+        a batch size is seen and replayed from then on.  The logits of a replayed step are
+        copied out of the graph's own output buffer, so they stay valid."""
+        key = (len(ids), tuple(want_rows))
+        entry = self._graphs.get(key)
+        if entry is None:
+            self._graphs[key] = "seen"
+            return self.model.forward(StepContext(self, plan, ids, want_rows))
+        if entry == "seen":
+            if len(self._graphs) > 64:
+                self._graphs = {k: v for k, v in self._graphs.items() if v == "seen"}
+            ctx = StepContext(self, plan, ids, want_rows)
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                out = self.model.forward(ctx)
+            launches = ops.launch_count() - before
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            self._graphs[key] = (graph, ctx, out, launches)
+            graph.replay()
+            return out.clone()
+        graph, ctx, out, launches = entry
+        StepContext(self, plan, ids, want_rows, into=ctx.buffer)
+        graph.replay()
+        ops.count_launches(launches)
+        return out.clone()
 
     def check_device_errors(self) -> None:
         """Read the kernels' error word (synchronises)."""

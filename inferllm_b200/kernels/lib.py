@@ -21,6 +21,8 @@ _SIGNATURES = {
     "illm_swiglu": [P, P, I, I, I, P],
     "illm_rope_kv_write": [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, P, P],
     "illm_attention_generic": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],
+    "illm_attention_decode": [P, I, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
+    "illm_attention_decode_supported": [I, I, I],
     "illm_gemm_f32_nt": [P, P, P, I, I, I, I, I, I, P],
     "illm_argmax": [P, I, I, I, P, P],
     "illm_sample": [P, I, I, I, P, P, I, F, F, I, F, P, P, P],

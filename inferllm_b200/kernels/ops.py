@@ -33,6 +33,12 @@ def launch_count() -> int:
     return _launches
 
 
+def count_launches(n: int) -> None:
+    """Account for kernels launched by replaying a captured graph."""
+    global _launches
+    _launches += n
+
+
 def _check(code, what):
     global _launches
     _launches += 1
@@ -169,9 +175,46 @@ def attention_generic(qkv, k_cache, v_cache, block_table, token_pos, token_seq, 
     return out
 
 
+DECODE_CHUNK = 256
+
+
+def attention_decode_supported(dtype, n_heads, n_kv_heads, head_dim, page_size) -> bool:
+    return dtype == torch.bfloat16 and n_heads % n_kv_heads == 0 and bool(
+        load().illm_attention_decode_supported(head_dim, n_heads // n_kv_heads, page_size))
+
+
+def attention_decode(qkv, k_cache, v_cache, block_table, token_pos, token_seq, n_heads, n_kv_heads,
+                     head_dim, page_size, window, scale, max_len):
+    """bfloat16 attention of single tokens, split over chunks of 256 keys and merged in a fixed
+    order.  `max_len` bounds the sequence lengths of the launch (it sizes the grid and the
+    scratch, not the result)."""
+    _need(qkv, "qkv", torch.bfloat16, 2)
+    _need(k_cache, "k_cache", torch.bfloat16, 4)
+    _need(v_cache, "v_cache", torch.bfloat16, 4)
+    T = qkv.shape[0]
+    n_chunks = max(1, -(-int(max_len) // DECODE_CHUNK))
+    part_acc = torch.empty((T, n_heads, n_chunks, head_dim), dtype=torch.float32, device=qkv.device)
+    part_ml = torch.empty((T, n_heads, n_chunks, 2), dtype=torch.float32, device=qkv.device)
+    out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    for t0 in range(0, T, 65535):
+        t1 = min(T, t0 + 65535)
+        _check(load().illm_attention_decode(
+            _ptr(qkv[t0:t1]), qkv.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+            block_table.shape[1], _ptr(token_pos[t0:t1]), _ptr(token_seq[t0:t1]), _ptr(part_acc[t0:t1]),
+            _ptr(part_ml[t0:t1]), _ptr(out[t0:t1]), t1 - t0, n_heads, n_kv_heads, head_dim, page_size,
+            int(window or 0), float(scale), n_chunks, _stream()), "attention_decode")
+    return out
+
+
 def attention(qkv, kv, ctx, n_heads, n_kv_heads, head_dim, window, scale):
     """Attention of the step's tokens over the cache entry `kv` (a KVView): picks the kernel
     for the dtype, head size and kind of step."""
+    if ctx.is_decode and attention_decode_supported(qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_size):
+        # grid and scratch are sized for the longest sequence the cache allows, so that the
+        # launch is the same at every step
+        return attention_decode(qkv, kv.k, kv.v, kv.block_table, ctx.token_pos, ctx.token_seq,
+                                n_heads, n_kv_heads, head_dim, kv.page_size, window, scale,
+                                ctx.max_seq_len)
     return attention_generic(qkv, kv.k, kv.v, kv.block_table, ctx.token_pos, ctx.token_seq,
                              n_heads, n_kv_heads, head_dim, kv.page_size, window, scale)
 

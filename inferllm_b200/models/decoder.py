@@ -84,6 +84,12 @@ class DecoderModel:
         y = self.final_norm.forward(stream, rows=ctx.want_rows)
         return self.head.forward(y)
 
+    def graph_safe(self) -> bool:
+        """True if a one-token-per-sequence step launches the same kernels every time, i.e. no
+        part reads host-side fields of the step context (a mixer says so with `graph_safe`)."""
+        return all(getattr(b.mixer, "graph_safe", False) and getattr(b.ffn, "graph_safe", True)
+                   for b in self.blocks)
+
     # ---- figures for the roofline
 
     def weight_bytes_per_step(self) -> int:

@@ -22,6 +22,8 @@ from .base import Mixer, PagedKV, TensorDecl, build_part, register_mixer
 
 @register_mixer("attention")
 class Attention(Mixer):
+    graph_safe = True   # a decode step's launches depend only on the batch size
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.hidden = int(spec["hidden_size"])

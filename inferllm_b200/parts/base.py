@@ -101,6 +101,12 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True promises that a one-token-per-sequence step launches the same kernels with the same
+    # arguments whenever the batch size is the same (everything that varies is read from device
+    # memory), so the engine may capture it in a CUDA graph.  A mixer that reads host-side
+    # fields of the step context (q_lens, past, ...) leaves it False.
+    graph_safe = False
+
     def cache_request(self):
         """`PagedKV`, `FixedState` or None."""
         return None

@@ -205,6 +205,43 @@ def test_attention_generic(dtype, nh, nkv, d, page, window):
         assert maxrel(got[idx], ref) <= (2e-6 if dtype == "float32" else 2 ** -7)
 
 
+@pytest.mark.parametrize("nh,nkv,d,page,window", [
+    (4, 4, 128, 64, None), (8, 2, 128, 16, None), (8, 1, 128, 64, None), (6, 2, 64, 8, None),
+    (3, 3, 64, 64, None), (16, 2, 64, 32, None), (4, 2, 128, 64, 300), (2, 1, 64, 4, 5)])
+def test_attention_decode(nh, nkv, d, page, window):
+    """The split-key decode kernel: sequences that end inside the first chunk, exactly on a chunk
+    border, and several chunks long."""
+    lens = [1, 255, 256, 257, 700, 1024, 3]
+    pc = Paged(lens, nkv, d, page, torch.bfloat16, seed=d + nh)
+    g = torch.Generator().manual_seed(3)
+    T = len(lens)
+    q = torch.randn(T, nh, d, generator=g).bfloat16()
+    qkv = torch.cat([q.reshape(T, nh * d), torch.zeros(T, 2 * nkv * d, dtype=torch.bfloat16)], dim=1)
+    seq = torch.arange(T, dtype=torch.int32)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    scale = 1.0 / math.sqrt(d)
+    assert ops.attention_decode_supported(torch.bfloat16, nh, nkv, d, page)
+    for max_len in (1024, 4096):      # the grid's size must not change the result
+        out = ops.attention_decode(dev(qkv), dev(pc.kc), dev(pc.vc), dev(pc.table), dev(pos), dev(seq),
+                                   nh, nkv, d, page, window, scale, max_len)
+        got = f64(out)
+        assert np.isfinite(got).all()
+        for b in range(T):
+            ref = plain_attention_rows(f64(q[b:b + 1]), f64(pc.k[b]), f64(pc.v[b]), [lens[b] - 1], nh, nkv, scale, window)
+            assert maxrel(got[b:b + 1], ref) <= 2 ** -7, f"sequence of {lens[b]} keys"
+    # a token's result does not depend on the rest of the batch
+    alone = ops.attention_decode(dev(qkv[4:5]), dev(pc.kc), dev(pc.vc), dev(pc.table[4:5]), dev(pos[4:5]),
+                                 dev(torch.zeros(1, dtype=torch.int32)), nh, nkv, d, page, window, scale, 4096)
+    assert torch.equal(alone[0].cpu(), out[4].cpu())
+
+
+def test_attention_decode_says_what_it_takes():
+    assert not ops.attention_decode_supported(torch.float32, 4, 4, 128, 64)
+    assert not ops.attention_decode_supported(torch.bfloat16, 4, 4, 24, 64)
+    assert not ops.attention_decode_supported(torch.bfloat16, 5, 1, 128, 64)
+    assert not ops.attention_decode_supported(torch.bfloat16, 4, 4, 128, 6)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_attention_finds_one_far_key_among_hundreds(dtype):
     """One key far back (first page) matches the query strongly: the output must be its value.
@@ -227,6 +264,11 @@ def test_attention_finds_one_far_key_among_hundreds(dtype):
                                     dev(torch.zeros(1, dtype=torch.int32)), nh, nkv, d, page, None, 1.0)
         want = f64(pc.v[0][target]).reshape(-1)
         assert maxrel(f64(out).reshape(-1), want) <= 1e-2, f"key {target} was not found"
+        if dtype == "bfloat16":
+            out = ops.attention_decode(dev(qkv), dev(kc), dev(vc), dev(pc.table),
+                                       dev(torch.tensor([n - 1], dtype=torch.int32)),
+                                       dev(torch.zeros(1, dtype=torch.int32)), nh, nkv, d, page, None, 1.0, 1024)
+            assert maxrel(f64(out).reshape(-1), want) <= 1e-2, f"decode kernel: key {target} was not found"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -47,9 +47,9 @@ class PartHarness:
         self._stage = None
         self._staging_busy = None
 
-    def _upload(self, parts, offs, total):
+    def _upload(self, parts, offs, total, into=None):
         from inferllm_b200.engine import Engine
-        return Engine._upload(self, parts, offs, total)
+        return Engine._upload(self, parts, offs, total, into)
 
     def context(self, slots, q_lens, ids=None, want=()):
         from inferllm_b200.engine import StepContext
