@@ -209,3 +209,64 @@ extern "C" int illm_attention_decode_supported(int d, int g, int page_size) {
     if (d == 64) return g == 1 || g == 2 || g == 3 || g == 4 || g == 8;
     return 0;
 }
+
+// ---- the entry point that allocates nothing (declared and described in no_alloc.h)
+
+#include <stdio.h>
+
+#include <mutex>
+
+#include "no_alloc.h"
+
+// Scratch of the static entry point: lives in the device image of this library on every GPU that
+// loads it.  In host code this name is only a handle for cudaGetSymbolAddress, not an address.
+static __device__ __align__(256) float g_static_scratch[ILLM_STATIC_SCRATCH_BYTES / sizeof(float)];
+
+#define ILLM_MAX_DEVICES 64
+static float* g_static_scratch_addr[ILLM_MAX_DEVICES];  // per device, filled at its first call
+static std::mutex g_static_scratch_mutex;
+
+static int static_scratch_for_current_device(float** ptr) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= ILLM_MAX_DEVICES) return ILLM_ERR_BAD_ARG;
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);   // the address on the current device
+        if (e != cudaSuccess) return (int)e;
+        g_static_scratch_addr[dev] = (float*)p;
+    }
+    *ptr = g_static_scratch_addr[dev];
+    return 0;
+}
+
+extern "C" int illm_attention_decode_static(const void* q, int q_stride, const void* kc, const void* vc,
+                                            const int* block_table, int max_pages, const int* token_pos,
+                                            const int* token_seq, void* out, int T, int nh, int nkv, int d,
+                                            int page_size, int window, float scale, int max_len,
+                                            char* err_msg, int err_len, void* stream) {
+    if (err_msg && err_len > 0) err_msg[0] = 0;
+    if (T <= 0) return 0;
+    if (max_len <= 0 || nh <= 0 || d <= 0) return ILLM_ERR_BAD_ARG;
+    const long long n_chunks = (max_len + AD_CHUNK - 1) / AD_CHUNK;
+    const long long need = (long long)T * nh * n_chunks * (d + 2) * (long long)sizeof(float);
+    if (need > (long long)ILLM_STATIC_SCRATCH_BYTES) {
+        if (err_msg && err_len > 0)
+            snprintf(err_msg, (size_t)err_len,
+                     "illm_attention_decode_static: %d tokens x %d heads x %lld chunks of keys need %lld "
+                     "bytes of scratch, the built-in array holds %u; split the call or use "
+                     "illm_attention_decode with scratch of your own",
+                     T, nh, n_chunks, need, (unsigned)ILLM_STATIC_SCRATCH_BYTES);
+        return ILLM_ERR_SCRATCH_TOO_SMALL;
+    }
+    float* scratch = nullptr;
+    int rc = static_scratch_for_current_device(&scratch);
+    if (rc != 0) return rc;
+    float* part_acc = scratch;
+    float* part_ml = scratch + (size_t)T * nh * n_chunks * d;
+    return illm_attention_decode(q, q_stride, kc, vc, block_table, max_pages, token_pos, token_seq,
+                                 part_acc, part_ml, out, T, nh, nkv, d, page_size, window, scale,
+                                 (int)n_chunks, stream);
+}
