@@ -13,6 +13,8 @@
 // leaves the cache alone (a layer that reads another layer's keys and values).
 #include "common.cuh"
 
+#define RK_SLOTS_PER_BLOCK 4
+
 template <typename TA>
 __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const float2* __restrict__ cs,
                                      const int* __restrict__ token_pos,
@@ -43,36 +45,30 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const float2* __restr
         return;
     }
     const size_t head_stride = (size_t)page_size * d;  // between kv heads inside a page
-    const int n_rot_heads = write_kv ? nh + nkv : nh;
+    // this block's share of the head slots: [q heads | k heads | v heads]
+    const int n_slots = nh + 2 * nkv;
+    const int s0 = blockIdx.y * RK_SLOTS_PER_BLOCK;
+    const int s1 = min(n_slots, s0 + RK_SLOTS_PER_BLOCK);
     const float2* cst = cs + (size_t)p * half;
-    for (int i = threadIdx.x; i < n_rot_heads * half; i += blockDim.x) {
-        const int head = i / half, j = i - head * half;
-        TA* src = row + (size_t)head * d;
-        const float a = to_f32(src[j]), b = to_f32(src[j + half]);
-        const float2 c = cst[j];
-        const float ra = a * c.x - b * c.y;
-        const float rb = a * c.y + b * c.x;
-        if (head < nh) {
-            src[j] = from_f32<TA>(ra);
-            src[j + half] = from_f32<TA>(rb);
-        } else {
-            TA* dst = kdst + (size_t)(head - nh) * head_stride;
-            dst[j] = from_f32<TA>(ra);
-            dst[j + half] = from_f32<TA>(rb);
-        }
-    }
-    if (!write_kv) return;
-    // K channels outside the rotated part
     const int rest = d - rot;
-    for (int i = threadIdx.x; i < nkv * rest; i += blockDim.x) {
-        const int hk = i / rest, c = rot + (i - hk * rest);
-        kdst[(size_t)hk * head_stride + c] = row[(size_t)(nh + hk) * d + c];
-    }
-    // V
-    const TA* vsrc = row + (size_t)(nh + nkv) * d;
-    for (int i = threadIdx.x; i < nkv * d; i += blockDim.x) {
-        const int hk = i / d, c = i - hk * d;
-        vdst[(size_t)hk * head_stride + c] = vsrc[i];
+    for (int slot = s0; slot < s1; slot++) {
+        TA* src = row + (size_t)slot * d;
+        if (slot < nh + nkv) {
+            const bool is_k = slot >= nh;
+            if (is_k && !write_kv) continue;
+            TA* dst = is_k ? kdst + (size_t)(slot - nh) * head_stride : src;
+            for (int j = threadIdx.x; j < half; j += blockDim.x) {
+                const float a = to_f32(src[j]), b = to_f32(src[j + half]);
+                const float2 c = cst[j];
+                dst[j] = from_f32<TA>(a * c.x - b * c.y);
+                dst[j + half] = from_f32<TA>(a * c.y + b * c.x);
+            }
+            if (is_k)   // K channels outside the rotated part
+                for (int c = rot + threadIdx.x; c < rot + rest; c += blockDim.x) dst[c] = src[c];
+        } else if (write_kv) {
+            TA* dst = vdst + (size_t)(slot - nh - nkv) * head_stride;
+            for (int c = threadIdx.x; c < d; c += blockDim.x) dst[c] = src[c];
+        }
     }
 }
 
@@ -84,14 +80,15 @@ extern "C" int illm_rope_kv_write(void* qkv, const float* cos_sin, const int* to
     if (T <= 0) return 0;
     if (rot < 0 || rot > d || (rot & 1) || (rot > 0 && cos_sin == nullptr)) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    int work = (nh + 2 * nkv) * d / 2;
-    int threads = work >= 2048 ? 256 : 128;
+    dim3 grid(T, (nh + 2 * nkv + RK_SLOTS_PER_BLOCK - 1) / RK_SLOTS_PER_BLOCK);
+    if (T > 2147483647 / 2 || grid.y > 65535) return ILLM_ERR_BAD_ARG;
+    int threads = d >= 128 ? 64 : 32;
     if (act_dtype == ILLM_BF16)
-        rope_kv_write_kernel<bf16><<<T, threads, 0, s>>>(
+        rope_kv_write_kernel<bf16><<<grid, threads, 0, s>>>(
             (bf16*)qkv, (const float2*)cos_sin, token_pos, token_seq, block_table, max_pages,
             (bf16*)kc, (bf16*)vc, nh, nkv, d, rot, page_size, write_kv, table_positions, err);
     else if (act_dtype == ILLM_F32)
-        rope_kv_write_kernel<float><<<T, threads, 0, s>>>(
+        rope_kv_write_kernel<float><<<grid, threads, 0, s>>>(
             (float*)qkv, (const float2*)cos_sin, token_pos, token_seq, block_table, max_pages,
             (float*)kc, (float*)vc, nh, nkv, d, rot, page_size, write_kv, table_positions, err);
     else
