@@ -62,4 +62,16 @@ __device__ __forceinline__ void load8(const float* p, float* f) {
     f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
 }
 
+__device__ __forceinline__ void store8(bf16* p, const float* f) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; i++) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ void store8(float* p, const float* f) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
+
 static inline int illm_launch_status() { return (int)cudaGetLastError(); }

@@ -39,9 +39,66 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restri
         o[c] = from_f32<TA>((row[c] * scale) * to_f32(w[c]));
 }
 
+// Rows of up to 8 * 8 * 256 elements (H a multiple of 8): the row stays in registers, 8
+// elements per thread and iteration with 16-byte accesses; same arithmetic as above.
+#define RN_THREADS 256
+template <typename TA, typename TW, int ITERS>
+__global__ void __launch_bounds__(RN_THREADS)
+add_rmsnorm_reg_kernel(float* __restrict__ resid, const TA* __restrict__ delta, const TW* __restrict__ w,
+                       TA* __restrict__ y, const int* __restrict__ rows, int H, float eps, int write_resid) {
+    __shared__ float scratch[32];
+    const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* x = resid + (size_t)r * H;
+    const TA* dl = delta ? delta + (size_t)r * H : nullptr;
+    float v[ITERS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITERS; i++) {
+        const int c = (threadIdx.x + i * RN_THREADS) * 8;
+        if (c < H) {
+            load8(x + c, v[i]);
+            if (dl) {
+                float d8[8];
+                load8(dl + c, d8);
+#pragma unroll
+                for (int k = 0; k < 8; k++) v[i][k] += d8[k];
+                if (write_resid) store8(x + c, v[i]);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; k++) ss += v[i][k] * v[i][k];
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = rsqrtf(ss / (float)H + eps);
+    TA* o = y + (size_t)blockIdx.x * H;
+#pragma unroll
+    for (int i = 0; i < ITERS; i++) {
+        const int c = (threadIdx.x + i * RN_THREADS) * 8;
+        if (c < H) {
+            float w8[8], r8[8];
+            load8(w + c, w8);
+#pragma unroll
+            for (int k = 0; k < 8; k++) r8[k] = (v[i][k] * scale) * w8[k];
+            store8(o + c, r8);
+        }
+    }
+}
+
 template <typename TA, typename TW>
 static int launch(float* resid, const void* delta, const void* w, void* y, const int* rows,
                   int n_rows, int H, float eps, int write_resid, cudaStream_t s) {
+    if ((H & 7) == 0 && H <= 8 * 8 * RN_THREADS) {
+        const int iters = (H / 8 + RN_THREADS - 1) / RN_THREADS;
+#define RN_CASE(N)                                                                                   \
+    add_rmsnorm_reg_kernel<TA, TW, N><<<n_rows, RN_THREADS, 0, s>>>(resid, (const TA*)delta, (const TW*)w, \
+                                                                   (TA*)y, rows, H, eps, write_resid)
+        if (iters <= 1) RN_CASE(1);
+        else if (iters <= 2) RN_CASE(2);
+        else if (iters <= 4) RN_CASE(4);
+        else RN_CASE(8);
+#undef RN_CASE
+        return illm_launch_status();
+    }
     size_t smem = (size_t)H * sizeof(float);
     if (smem > 200 * 1024) return ILLM_ERR_BAD_ARG;
     auto kern = add_rmsnorm_kernel<TA, TW>;

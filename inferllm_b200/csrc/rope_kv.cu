@@ -13,7 +13,7 @@
 // leaves the cache alone (a layer that reads another layer's keys and values).
 #include "common.cuh"
 
-#define RK_SLOTS_PER_BLOCK 4
+#define RK_SLOTS_PER_BLOCK 4   // one warp per block, one head slot after the other
 
 template <typename TA>
 __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const float2* __restrict__ cs,
@@ -51,23 +51,55 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const float2* __restr
     const int s1 = min(n_slots, s0 + RK_SLOTS_PER_BLOCK);
     const float2* cst = cs + (size_t)p * half;
     const int rest = d - rot;
+    // 8 channels per thread with 16-byte accesses where the sizes allow it
+    const bool vec = ((half & 7) == 0) && ((d & 7) == 0) && ((rot & 7) == 0);
     for (int slot = s0; slot < s1; slot++) {
         TA* src = row + (size_t)slot * d;
         if (slot < nh + nkv) {
             const bool is_k = slot >= nh;
             if (is_k && !write_kv) continue;
             TA* dst = is_k ? kdst + (size_t)(slot - nh) * head_stride : src;
-            for (int j = threadIdx.x; j < half; j += blockDim.x) {
-                const float a = to_f32(src[j]), b = to_f32(src[j + half]);
-                const float2 c = cst[j];
-                dst[j] = from_f32<TA>(a * c.x - b * c.y);
-                dst[j + half] = from_f32<TA>(a * c.y + b * c.x);
+            if (vec) {
+                for (int j = threadIdx.x * 8; j < half; j += blockDim.x * 8) {
+                    float a[8], b[8], ra[8], rb[8];
+                    load8(src + j, a);
+                    load8(src + j + half, b);
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        const float2 c = cst[j + k];
+                        ra[k] = a[k] * c.x - b[k] * c.y;
+                        rb[k] = a[k] * c.y + b[k] * c.x;
+                    }
+                    store8(dst + j, ra);
+                    store8(dst + j + half, rb);
+                }
+                if (is_k)
+                    for (int c = rot + threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+                        float a[8];
+                        load8(src + c, a);
+                        store8(dst + c, a);
+                    }
+            } else {
+                for (int j = threadIdx.x; j < half; j += blockDim.x) {
+                    const float a = to_f32(src[j]), b = to_f32(src[j + half]);
+                    const float2 c = cst[j];
+                    dst[j] = from_f32<TA>(a * c.x - b * c.y);
+                    dst[j + half] = from_f32<TA>(a * c.y + b * c.x);
+                }
+                if (is_k)   // K channels outside the rotated part
+                    for (int c = rot + threadIdx.x; c < rot + rest; c += blockDim.x) dst[c] = src[c];
             }
-            if (is_k)   // K channels outside the rotated part
-                for (int c = rot + threadIdx.x; c < rot + rest; c += blockDim.x) dst[c] = src[c];
         } else if (write_kv) {
             TA* dst = vdst + (size_t)(slot - nh - nkv) * head_stride;
-            for (int c = threadIdx.x; c < d; c += blockDim.x) dst[c] = src[c];
+            if (vec) {
+                for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+                    float a[8];
+                    load8(src + c, a);
+                    store8(dst + c, a);
+                }
+            } else {
+                for (int c = threadIdx.x; c < d; c += blockDim.x) dst[c] = src[c];
+            }
         }
     }
 }
@@ -82,7 +114,7 @@ extern "C" int illm_rope_kv_write(void* qkv, const float* cos_sin, const int* to
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(T, (nh + 2 * nkv + RK_SLOTS_PER_BLOCK - 1) / RK_SLOTS_PER_BLOCK);
     if (T > 2147483647 / 2 || grid.y > 65535) return ILLM_ERR_BAD_ARG;
-    int threads = d >= 128 ? 64 : 32;
+    int threads = 32;
     if (act_dtype == ILLM_BF16)
         rope_kv_write_kernel<bf16><<<grid, threads, 0, s>>>(
             (bf16*)qkv, (const float2*)cos_sin, token_pos, token_seq, block_table, max_pages,

@@ -18,10 +18,38 @@ __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, i
     }
 }
 
+// 8 elements per thread with 16-byte loads (I a multiple of 8).
+template <typename TA>
+__global__ void swiglu_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, long long n_vec) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_vec) return;
+    const int per_row = I / 8;
+    const long long t = i / per_row;
+    const int c = (int)(i - t * per_row) * 8;
+    float a[8], b[8];
+    load8(gu + t * 2 * I + c, a);
+    load8(gu + t * 2 * I + I + c, b);
+    float r[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) r[k] = (a[k] / (1.0f + expf(-a[k]))) * b[k];
+    store8(out + t * I + c, r);
+}
+
 extern "C" int illm_swiglu(const void* gu, void* out, int act_dtype, int T, int I, void* stream) {
     if (T <= 0 || I <= 0) return 0;
     if (T > 65535 * 32) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
+    if ((I & 7) == 0) {
+        const long long n_vec = (long long)T * (I / 8);
+        const unsigned blocks = (unsigned)((n_vec + 255) / 256);
+        if (act_dtype == ILLM_BF16)
+            swiglu_vec_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)gu, (bf16*)out, I, n_vec);
+        else if (act_dtype == ILLM_F32)
+            swiglu_vec_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, (float*)out, I, n_vec);
+        else
+            return ILLM_ERR_BAD_ARG;
+        return illm_launch_status();
+    }
     // grid.y is limited to 65535: fold larger T into several launches
     for (int t0 = 0; t0 < T; t0 += 65535) {
         int n = T - t0 < 65535 ? T - t0 : 65535;
