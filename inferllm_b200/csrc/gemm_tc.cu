@@ -1,0 +1,327 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:  C[M, N] = X[M, K] . W[N, K]^T
+// with float32 accumulation in tensor memory.
+//
+// Both operands are K-major (rows contiguous in K), which is how activations [tokens, K] and
+// weights [out, in] lie in memory, so neither is ever transposed (the reference calls
+// cublasSgemm(OP_T, OP_N, ...) on the same layouts, src/kern/gpu/kernel_gpu.cu:420-435; formula
+// src/kern/naive/naive.cpp:363-379).
+//
+// One block computes a tile D[128, BN] = A[128 rows, K-range] . B[BN rows, K-range]^T:
+//   warp 0   one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of [128 x 64] and
+//            [BN x 64] operand tiles into a ring of shared-memory stages, arming a "full" mbarrier
+//            per stage with the byte count;
+//   warp 1   owns the tensor memory (tcgen05.alloc) and one thread issues tcgen05.mma
+//            (M = 128, N = BN, K = 16, four per stage), then tcgen05.commit on the stage's "empty"
+//            barrier so that the loader may refill it, and on a last barrier for the epilogue;
+//   warps 2-5 read the accumulators with tcgen05.ld (a thread per row of the tile) and store.
+// Two orientations share the kernel.  Prompts (many tokens): A = X, B = W, BN up to 256, a thread
+// stores a row of C.  Decoding (at most 64 tokens): A = W, B = X ("swap"), so that the weight rows
+// fill the 128 lanes of the MMA and the few tokens are its N; a warp then stores 32 consecutive
+// outputs of one token.  For decoding the K range is also split over blockIdx.z, so that some 300
+// blocks stream the weights with every SM busy; the partial sums go to a workspace and a second
+// kernel adds them in ascending order of the split (the result does not depend on timing).
+// Rows beyond M or N and columns beyond K are zero-filled by the TMA unit, so any M, any N and
+// any K that is a multiple of 8 (the 16-byte stride rule of tensor maps) is taken.
+// Every wait on an mbarrier is bounded: after the limit the thread raises the error word and
+// goes on, so a fault in the pipeline ends the kernel instead of hanging the GPU.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define TC_WAIT_LIMIT (1 << 22)
+#define TC_ERR_TIMEOUT 4
+
+__device__ __forceinline__ unsigned tc_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false (and the error word set) on time-out.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* err) {
+    for (int i = 0; i < TC_WAIT_LIMIT; i++) {
+        unsigned ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (i > 64) __nanosleep(32);
+    }
+    atomicExch(err, TC_ERR_TIMEOUT);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled:
+// 8-row groups 1024 bytes apart (stride byte offset), leading byte offset unused (1), version 1.
+__device__ __forceinline__ unsigned long long umma_desc_sw128(unsigned smem_addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_addr & 0x3FFFF) >> 4);
+    d |= (unsigned long long)1 << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long da, unsigned long long db,
+                                          unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, float* v) {
+    unsigned r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+
+template <typename TOut> __device__ __forceinline__ void store_out(TOut* p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// D[ra, rb] = sum_k A[ra, k] B[rb, k];  SWAP = false: C[ra * ldc + rb];  SWAP = true: C[rb * ldc + ra].
+template <int BN, int STAGES, bool SWAP, typename TOut>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               TOut* __restrict__ C, long long split_stride, int ldc, int RA, int RB, int k_iters_total,
+               int k_iters_per_split, int* __restrict__ err) {
+    constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
+    constexpr unsigned TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
+    __shared__ unsigned tmem_holder;
+
+    // operand tiles start on a 1024-byte boundary of the shared window (the swizzle's period)
+    const unsigned a_base = (tc_smem_u32(smem_raw) + 1023u) & ~1023u, b_base = a_base + STAGES * A_BYTES;
+    const unsigned full0 = tc_smem_u32(&bars[0]), empty0 = tc_smem_u32(&bars[STAGES]);
+    const unsigned done_bar = tc_smem_u32(&bars[2 * STAGES]);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ra0 = blockIdx.x * TC_BM, rb0 = blockIdx.y * BN;
+    const int k_begin = blockIdx.z * k_iters_per_split;
+    int k_end = k_begin + k_iters_per_split;
+    if (k_end > k_iters_total) k_end = k_iters_total;
+    const int n_k = k_end - k_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(done_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(tc_smem_u32(&tmem_holder)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool alive = true;
+            for (int i = 0; i < n_k && alive; i++) {
+                const int s = i % STAGES;
+                if (i >= STAGES) alive = mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, err);
+                if (!alive) break;
+                mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
+                const int kx = (k_begin + i) * TC_BK;
+                tma_load_2d(a_base + s * A_BYTES, &map_a, kx, ra0, full0 + 8 * s);
+                tma_load_2d(b_base + s * B_BYTES, &map_b, kx, rb0, full0 + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool alive = true;
+            for (int i = 0; i < n_k && alive; i++) {
+                const int s = i % STAGES;
+                alive = mbar_wait(full0 + 8 * s, (i / STAGES) & 1, err);
+                if (!alive) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; kk++) {
+                    const unsigned long long da = umma_desc_sw128(a_base + s * A_BYTES + kk * 32);
+                    const unsigned long long db = umma_desc_sw128(b_base + s * B_BYTES + kk * 32);
+                    umma_bf16(tmem, da, db, IDESC, (i > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(empty0 + 8 * s);   // arrives when these MMAs have read the stage
+            }
+            umma_commit(done_bar);             // arrives when every MMA of the tile is done
+        }
+    } else {
+        // epilogue: warp w may touch the 32 lanes of tensor memory of its quadrant w % 4
+        const int quad = warp & 3;
+        const bool ok = mbar_wait(done_bar, 0, err);
+        tc_fence_after();
+        const int ra = ra0 + quad * 32 + lane;
+        TOut* Cz = C + (size_t)blockIdx.z * split_stride;
+        if (ok && n_k > 0) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (rb0 + c0 >= RB) break;   // uniform over the warp
+                float v[16];
+                tmem_ld16(tmem + ((unsigned)(quad * 32) << 16) + (unsigned)c0, v);
+                if (SWAP) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const int rb = rb0 + c0 + j;
+                        if (rb < RB && ra < RA) store_out<TOut>(Cz + (size_t)rb * ldc + ra, v[j]);
+                    }
+                } else if (ra < RA) {
+                    TOut* dst = Cz + (size_t)ra * ldc + rb0 + c0;
+                    if (rb0 + c0 + 16 <= RB && ((ldc & 7) == 0)) {
+                        store8(dst, v);
+                        store8(dst + 8, v + 8);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            if (rb0 + c0 + j < RB) store_out<TOut>(dst + j, v[j]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// C[i] = sum over splits (ascending) of partial[s][i]
+template <typename TOut>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, TOut* __restrict__ C, long long n, int splits) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float acc = 0.f;
+    for (int s = 0; s < splits; s++) acc += partial[(size_t)s * n + i];
+    store_out<TOut>(C + i, acc);
+}
+
+// ---- host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// Tensor map of a row-major bfloat16 matrix [rows, K]; boxes of [box_rows, 64], 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return ILLM_ERR_BAD_ARG;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : ILLM_ERR_BAD_ARG;
+}
+
+template <int BN, int STAGES, bool SWAP, typename TOut>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TOut* C, long long split_stride, int ldc,
+                     int RA, int RB, int k_iters, int splits, int* err, cudaStream_t s) {
+    const size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+    auto kern = gemm_tc_kernel<BN, STAGES, SWAP, TOut>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    const int per_split = (k_iters + splits - 1) / splits;
+    dim3 grid((RA + TC_BM - 1) / TC_BM, (RB + BN - 1) / BN, splits);
+    kern<<<grid, TC_THREADS, smem, s>>>(ma, mb, C, split_stride, ldc, RA, RB, k_iters, per_split, err);
+    return illm_launch_status();
+}
+
+template <typename TOut>
+static int run_tc(const void* X, const void* W, TOut* out, int M, int N, int K, float* ws, int splits, int* err,
+                  cudaStream_t s) {
+    const int k_iters = (K + TC_BK - 1) / TC_BK;
+    CUtensorMap ma, mb;
+    int rc;
+    if (M <= 64) {
+        // decoding: A = W (its rows on the 128 lanes), B = X, out[m * N + n]
+        const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+        if ((rc = make_map(&ma, W, N, K, TC_BM)) != 0) return rc;
+        if ((rc = make_map(&mb, X, M, K, bn)) != 0) return rc;
+        if (splits > 1) {
+            // every split must own at least one K slice
+            const int per = (k_iters + splits - 1) / splits;
+            splits = (k_iters + per - 1) / per;
+        }
+        if (splits > 1) {
+            const long long n = (long long)M * N;
+            if (bn == 16) rc = launch_tc<16, 4, true, float>(ma, mb, ws, n, N, N, M, k_iters, splits, err, s);
+            else if (bn == 32) rc = launch_tc<32, 4, true, float>(ma, mb, ws, n, N, N, M, k_iters, splits, err, s);
+            else rc = launch_tc<64, 4, true, float>(ma, mb, ws, n, N, N, M, k_iters, splits, err, s);
+            if (rc != 0) return rc;
+            splitk_reduce_kernel<TOut><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(ws, out, n, splits);
+            return illm_launch_status();
+        }
+        if (bn == 16) return launch_tc<16, 4, true, TOut>(ma, mb, out, 0, N, N, M, k_iters, 1, err, s);
+        if (bn == 32) return launch_tc<32, 4, true, TOut>(ma, mb, out, 0, N, N, M, k_iters, 1, err, s);
+        return launch_tc<64, 4, true, TOut>(ma, mb, out, 0, N, N, M, k_iters, 1, err, s);
+    }
+    // prompts: A = X (tokens on the lanes), B = W
+    if ((rc = make_map(&ma, X, M, K, TC_BM)) != 0) return rc;
+    if (N >= 256) {
+        if ((rc = make_map(&mb, W, N, K, 256)) != 0) return rc;
+        return launch_tc<256, 4, false, TOut>(ma, mb, out, 0, N, M, N, k_iters, 1, err, s);
+    }
+    if ((rc = make_map(&mb, W, N, K, 128)) != 0) return rc;
+    return launch_tc<128, 4, false, TOut>(ma, mb, out, 0, N, M, N, k_iters, 1, err, s);
+}
+
+// out_dtype: ILLM_BF16 or ILLM_F32.  `ws`: float workspace of splits * M * N elements (splits > 1
+// is honoured for M <= 64 only).  X and W must be 16-byte aligned, K a multiple of 8.
+extern "C" int illm_gemm_bf16_tc(const void* X, const void* W, void* out, int out_dtype, int M, int N, int K,
+                                 float* ws, int splits, int* err, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K & 7) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || splits < 1) return ILLM_ERR_BAD_ARG;
+    if (splits > 1 && ws == nullptr) return ILLM_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == ILLM_BF16) return run_tc<bf16>(X, W, (bf16*)out, M, N, K, ws, splits, err, s);
+    if (out_dtype == ILLM_F32) return run_tc<float>(X, W, (float*)out, M, N, K, ws, splits, err, s);
+    return ILLM_ERR_BAD_ARG;
+}

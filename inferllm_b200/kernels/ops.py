@@ -259,6 +259,58 @@ def gemm_f32(x, w):
     return out
 
 
+_tc_err = {}
+N_SMS = 148
+
+
+def tc_error_word(device):
+    """The error word of the tensor-core GEMM's bounded waits (one per device)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _tc_err:
+        _tc_err[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_err[key]
+
+
+def gemm_tc_splits(M, N, K):
+    """How many slices of K a decode-sized product (M <= 64) is cut into, so that about two
+    blocks per SM stream the weights; 1 for larger M."""
+    if M > 64:
+        return 1
+    tiles = -(-N // 128)
+    k_iters = -(-K // 64)
+    return max(1, min(2 * N_SMS // tiles, k_iters // 8))
+
+
+def gemm_bf16_tc(x, w, out_dtype=torch.bfloat16):
+    """bfloat16 x [M, K] . w [N, K]^T on tcgen05 tensor cores, float32 accumulation."""
+    _need(x, "x", torch.bfloat16, 2)
+    _need(w, "w", torch.bfloat16, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"gemm: x is [{M}, {K}] but w is {tuple(w.shape)}")
+    if K % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
+        raise KernelError(f"gemm_bf16_tc: K = {K} must be a multiple of 8 and the operands 16-byte aligned")
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    splits = gemm_tc_splits(M, N, K)
+    ws = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
+    _check(load().illm_gemm_bf16_tc(_ptr(x), _ptr(w), _ptr(out), act_code(out_dtype), M, N, K, _ptr(ws),
+                                    splits, _ptr(tc_error_word(x.device)), _stream()), "gemm_bf16_tc")
+    return out
+
+
+_GEMM_BACKEND = "library"
+
+
+def set_gemm_backend(name: str) -> None:
+    """"tc": the package's tcgen05 kernel for every bfloat16 product it can take; "library":
+    cuBLAS through torch.mm."""
+    global _GEMM_BACKEND
+    if name not in ("tc", "library"):
+        raise ValueError("gemm backend must be 'tc' or 'library'")
+    _GEMM_BACKEND = name
+
+
 def linear(x, w, out_dtype=None):
     """x [M, K] . w [N, K]^T.  float32: the package's own FMA kernel.  bfloat16: the library
     product with float32 accumulation, rounded to bfloat16 or kept float32 (`out_dtype`)."""
@@ -266,6 +318,8 @@ def linear(x, w, out_dtype=None):
         return gemm_f32(x, w)
     _need(x, "x", torch.bfloat16, 2)
     _need(w, "w", torch.bfloat16, 2)
+    if _GEMM_BACKEND == "tc" and x.shape[1] % 8 == 0 and x.shape[0] > 0:
+        return gemm_bf16_tc(x, w, out_dtype or torch.bfloat16)
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     return torch.mm(x, w.t())

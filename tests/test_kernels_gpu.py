@@ -136,6 +136,33 @@ def test_linear_bf16(M, N, K):
     assert out.dtype == torch.bfloat16 and maxrel(f64(out), ref) <= 2 ** -8
 
 
+@pytest.mark.parametrize("M,N,K", [
+    (1, 128, 64), (8, 4096, 4096), (3, 200, 72), (16, 130, 512), (17, 384, 1000), (64, 1000, 320),
+    (65, 256, 64), (128, 256, 128), (300, 520, 328), (2048, 777, 200), (130, 100, 4096), (1, 32000, 256)])
+@pytest.mark.parametrize("out", ["bfloat16", "float32"])
+def test_gemm_bf16_tc(M, N, K, out):
+    """The tcgen05 product: token counts on both sides of the decode/prompt switch, sizes that
+    are no multiple of any tile, K with a ragged last slice, split K."""
+    g = torch.Generator().manual_seed(M + N + K)
+    x, w = torch.randn(M, K, generator=g).bfloat16(), torch.randn(N, K, generator=g).bfloat16()
+    got = ops.gemm_bf16_tc(dev(x), dev(w), DT[out])
+    assert got.dtype == DT[out] and tuple(got.shape) == (M, N)
+    ref = plain.linear(f64(x), f64(w))
+    assert maxrel(f64(got), ref) <= (2e-6 * math.sqrt(K) if out == "float32" else 2 ** -8)
+    assert int(ops.tc_error_word(got.device).item()) == 0
+
+
+def test_gemm_bf16_tc_rows_do_not_depend_on_the_batch():
+    g = torch.Generator().manual_seed(1)
+    x, w = torch.randn(40, 1024, generator=g).bfloat16(), torch.randn(512, 1024, generator=g).bfloat16()
+    full = ops.gemm_bf16_tc(dev(x), dev(w), torch.float32).cpu()
+    one = ops.gemm_bf16_tc(dev(x[7:8]), dev(w), torch.float32).cpu()
+    # same split of K and same order of accumulation whatever the number of tokens up to 64
+    assert torch.equal(one[0], full[7])
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+        ops.gemm_bf16_tc(dev(x[:, :1020]), dev(w[:, :1020]))
+
+
 # ---- rope + cache write, attention: a hand-made paged cache
 
 
