@@ -170,7 +170,9 @@ def forward(config: dict, weights: dict, ids, return_hidden=False):
         h = rms_norm(x, weights[p + "post_attention_layernorm.weight"], eps)
         x = x + swiglu_ffn(h, weights[p + "mlp.gate_proj.weight"],
                            weights[p + "mlp.up_proj.weight"], weights[p + "mlp.down_proj.weight"])
-    y = rms_norm(x, weights["model.norm.weight"], eps)
+    # the reference's head has an eps of its own (1e-5, src/core/graph.h:160-163); a config.json
+    # has one eps for all norms, so the extra key exists only for the comparison with the reference
+    y = rms_norm(x, weights["model.norm.weight"], config.get("final_norm_eps", eps))
     head = weights["model.embed_tokens.weight"] if config.get("tie_word_embeddings", False) \
         else weights["lm_head.weight"]
     logits = linear(y, head)
