@@ -127,6 +127,8 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--only", choices=["decode", "prefill"], help="run one scenario (for profiling); "
                     "prints a short JSON line of that scenario only")
+    ap.add_argument("--gemm", default="auto", choices=["auto", "tc", "library"])
+    ap.add_argument("--no-pdl", action="store_true", help="launch kernels without programmatic dependent launch")
     ap.add_argument("--context", type=int, default=CONTEXT, help="position at which the timed decode steps end")
     args = ap.parse_args()
 
@@ -160,6 +162,9 @@ def main():
     max_tokens = max(B * CONTEXT, 64 * (-(-(512 + decode_room) // 64) * 64), PREFILL_TOKENS) + 64
     model = Model(ModelConfig(compt_type="bfloat16", nr_ctx=CONTEXT, max_tokens=max_tokens, max_batch=max(B, 64)))
     model.load_random(cfg, seed=0)
+    ops.set_gemm_backend(args.gemm)
+    if args.no_pdl:
+        ops.set_pdl(False)
     model.init(top_k=0, top_p=1.0, temp=0.0, repeat_penalty=1.0, repeat_last_n=0, seed=0, end_token=-1)
     eng = model.engine
     g = torch.Generator().manual_seed(0)

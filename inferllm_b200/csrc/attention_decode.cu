@@ -29,6 +29,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
                         const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                         float* __restrict__ part_acc, float* __restrict__ part_ml, int n_chunks, int nh,
                         int nkv, int page_size, int window, float scale_log2e) {
+    pdl_grid_sync();
     constexpr int LPK = D / 8;                 // lanes per key
     constexpr int GROUPS = AD_THREADS / LPK;   // independent softmax streams in the block
     const int chunk = blockIdx.x, hk = blockIdx.y, t = blockIdx.z;
@@ -152,6 +153,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_acc
                                               const float* __restrict__ part_ml,
                                               const int* __restrict__ token_pos, bf16* __restrict__ out,
                                               int n_chunks, int nh, int window) {
+    pdl_grid_sync();
     const int h = blockIdx.x, t = blockIdx.y, c = threadIdx.x;
     const int p = token_pos[t];
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
@@ -174,10 +176,10 @@ static int launch(const void* q, int q_stride, const void* kc, const void* vc, c
                   float* part_ml, void* out, int T, int nh, int nkv, int page_size, int window,
                   float scale, int n_chunks, cudaStream_t s) {
     dim3 grid(n_chunks, nkv, T);
-    attention_decode_kernel<D, G><<<grid, AD_THREADS, 0, s>>>(
+    illm_launch(attention_decode_kernel<D, G>, dim3(grid), dim3(AD_THREADS), 0, s, 
         (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, block_table, max_pages, token_pos,
         token_seq, part_acc, part_ml, n_chunks, nh, nkv, page_size, window, scale * 1.4426950408889634f);
-    attention_decode_merge_kernel<D><<<dim3(nh, T), D, 0, s>>>(part_acc, part_ml, token_pos, (bf16*)out,
+    illm_launch(attention_decode_merge_kernel<D>, dim3(dim3(nh, T)), dim3(D), 0, s, part_acc, part_ml, token_pos, (bf16*)out,
                                                              n_chunks, nh, window);
     return illm_launch_status();
 }

@@ -28,6 +28,7 @@ attention_generic_kernel(const TA* __restrict__ q, int q_stride, const TA* __res
                          int max_pages, const int* __restrict__ token_pos,
                          const int* __restrict__ token_seq, TA* __restrict__ out, int nh, int nkv,
                          int d, int page_size, int window, float scale) {
+    pdl_grid_sync();
     extern __shared__ float smem[];
     float* qs = smem;                 // [d]
     float* acc_s = smem + d;          // [AG_WARPS][d]
@@ -127,11 +128,11 @@ extern "C" int illm_attention_generic(const void* q, int q_stride, const void* k
     dim3 grid(T, nh);
     size_t smem = (size_t)(1 + AG_WARPS) * d * sizeof(float);
     if (act_dtype == ILLM_BF16)
-        attention_generic_kernel<bf16><<<grid, AG_WARPS * 32, smem, s>>>(
+        illm_launch(attention_generic_kernel<bf16>, dim3(grid), dim3(AG_WARPS * 32), smem, s, 
             (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, block_table, max_pages,
             token_pos, token_seq, (bf16*)out, nh, nkv, d, page_size, window, scale);
     else if (act_dtype == ILLM_F32)
-        attention_generic_kernel<float><<<grid, AG_WARPS * 32, smem, s>>>(
+        illm_launch(attention_generic_kernel<float>, dim3(grid), dim3(AG_WARPS * 32), smem, s, 
             (const float*)q, q_stride, (const float*)kc, (const float*)vc, block_table, max_pages,
             token_pos, token_seq, (float*)out, nh, nkv, d, page_size, window, scale);
     else

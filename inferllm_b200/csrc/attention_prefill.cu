@@ -63,6 +63,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
                          const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
                          bf16* __restrict__ out, int nh, int nkv, int page_size, int window,
                          float scale_log2e) {
+    pdl_grid_sync();
     constexpr int CH = D / 8;       // 16-byte chunks per row
     constexpr int KS = D / 16;      // k-steps of Q K^T
     constexpr int NT_D = D / 8;     // n-tiles of the output
@@ -256,7 +257,7 @@ static int launch(const void* q, int q_stride, const void* kc, const void* vc, c
         if (e != cudaSuccess) return (int)e;
     }
     dim3 grid((max_q + FA_BM - 1) / FA_BM, nh, B);
-    kern<<<grid, FA_THREADS, smem, s>>>((const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, block_table,
+    illm_launch(kern, dim3(grid), dim3(FA_THREADS), smem, s, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, block_table,
                                         max_pages, cu_q, seq_lens, (bf16*)out, nh, nkv, page_size, window,
                                         scale * 1.4426950408889634f);
     return illm_launch_status();

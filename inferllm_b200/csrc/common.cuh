@@ -74,4 +74,33 @@ __device__ __forceinline__ void store8(float* p, const float* f) {
     *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
 }
 
+// Programmatic dependent launch.  Every kernel of the package starts with pdl_grid_sync(): it
+// waits until the kernels before it in the stream have finished and their writes are visible,
+// then lets the kernel after it begin to launch.  With the launch attribute below, a kernel's
+// blocks are therefore set up (scheduling, shared memory, barriers) while its predecessor is still
+// draining, which hides most of the gap between the many short kernels of a decode step.
+// Without the attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_grid_sync() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+inline int g_illm_pdl = 1;   // illm_set_pdl() switches the launch attribute off (e.g. for profilers)
+
+template <typename... KArgs, typename... Args>
+static inline void illm_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                               Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_illm_pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 static inline int illm_launch_status() { return (int)cudaGetLastError(); }

@@ -8,6 +8,7 @@
 template <typename TW>
 __global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                                  float* __restrict__ out, int H, int V, int* __restrict__ err) {
+    pdl_grid_sync();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * H;
@@ -35,10 +36,16 @@ extern "C" int illm_embedding(const int* ids, const void* table, int table_dtype
     cudaStream_t s = (cudaStream_t)stream;
     int threads = H >= 2048 ? 256 : 128;
     if (table_dtype == ILLM_BF16)
-        embedding_kernel<bf16><<<T, threads, 0, s>>>(ids, (const bf16*)table, out, H, V, err);
+        illm_launch(embedding_kernel<bf16>, dim3(T), dim3(threads), 0, s, ids, (const bf16*)table, out, H, V, err);
     else if (table_dtype == ILLM_F32)
-        embedding_kernel<float><<<T, threads, 0, s>>>(ids, (const float*)table, out, H, V, err);
+        illm_launch(embedding_kernel<float>, dim3(T), dim3(threads), 0, s, ids, (const float*)table, out, H, V, err);
     else
         return ILLM_ERR_BAD_ARG;
     return illm_launch_status();
+}
+
+// Switches programmatic dependent launch of all kernels of the library on (1, default) or off (0).
+extern "C" int illm_set_pdl(int on) {
+    g_illm_pdl = on ? 1 : 0;
+    return 0;
 }

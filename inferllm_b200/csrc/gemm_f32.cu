@@ -15,6 +15,7 @@
 __global__ void __launch_bounds__(256)
 gemm_f32_nt_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C,
                    int M, int N, int K, int lda, int ldw, int ldc) {
+    pdl_grid_sync();
     __shared__ __align__(16) float As[GF_BK][GF_BM + 4];
     __shared__ __align__(16) float Ws[GF_BK][GF_BN + 4];
     const int tid = threadIdx.x;
@@ -90,6 +91,6 @@ extern "C" int illm_gemm_f32_nt(const float* A, const float* W, float* C, int M,
     if (K <= 0) return ILLM_ERR_BAD_ARG;
     dim3 grid((N + GF_BN - 1) / GF_BN, (M + GF_BM - 1) / GF_BM);
     if (grid.y > 65535) return ILLM_ERR_BAD_ARG;
-    gemm_f32_nt_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
+    illm_launch(gemm_f32_nt_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, A, W, C, M, N, K, lda, ldw, ldc);
     return illm_launch_status();
 }

@@ -104,22 +104,24 @@ template <> __device__ __forceinline__ void store_out<float>(float* p, float v) 
 template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
 // D[ra, rb] = sum_k A[ra, k] B[rb, k];  SWAP = false: C[ra * ldc + rb];  SWAP = true: C[rb * ldc + ra].
-template <int BN, int STAGES, bool SWAP, typename TOut>
+#define TC_MAX_STAGES 12
+
+template <int BN, bool SWAP, typename TOut>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                TOut* __restrict__ C, long long split_stride, int ldc, int RA, int RB, int k_iters_total,
-               int k_iters_per_split, int* __restrict__ err) {
+               int k_iters_per_split, int STAGES, int* __restrict__ err) {
     constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
     constexpr unsigned TMEM_COLS = BN < 32 ? 32 : BN;
     constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
+    __shared__ __align__(8) unsigned long long bars[2 * TC_MAX_STAGES + 1];
     __shared__ unsigned tmem_holder;
 
     // operand tiles start on a 1024-byte boundary of the shared window (the swizzle's period)
     const unsigned a_base = (tc_smem_u32(smem_raw) + 1023u) & ~1023u, b_base = a_base + STAGES * A_BYTES;
-    const unsigned full0 = tc_smem_u32(&bars[0]), empty0 = tc_smem_u32(&bars[STAGES]);
-    const unsigned done_bar = tc_smem_u32(&bars[2 * STAGES]);
+    const unsigned full0 = tc_smem_u32(&bars[0]), empty0 = tc_smem_u32(&bars[TC_MAX_STAGES]);
+    const unsigned done_bar = tc_smem_u32(&bars[2 * TC_MAX_STAGES]);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ra0 = blockIdx.x * TC_BM, rb0 = blockIdx.y * BN;
@@ -146,6 +148,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = tmem_holder;
+    // everything above (barriers, tensor memory) was set up while the previous kernel drained;
+    // from here on global memory is touched
+    pdl_grid_sync();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -222,6 +227,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // C[i] = sum over splits (ascending) of partial[s][i]
 template <typename TOut>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TOut* __restrict__ C, long long n, int splits) {
+    pdl_grid_sync();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     float acc = 0.f;
@@ -261,17 +267,38 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
     return r == CUDA_SUCCESS ? 0 : ILLM_ERR_BAD_ARG;
 }
 
-template <int BN, int STAGES, bool SWAP, typename TOut>
+static int g_tc_stages_override = 0;   // set through illm_gemm_bf16_tc_tune, for measurements
+
+// Stages of the operand ring: as many bytes in flight per SM as its shared memory allows, shared
+// between the blocks that will be resident on it together.
+static int pick_stages(int stage_bytes, long long n_blocks, int k_iters_per_block) {
+    if (g_tc_stages_override > 0) return g_tc_stages_override;
+    const int per_sm = (int)((n_blocks + 147) / 148);
+    const int resident = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
+    int stages = (216 * 1024 / resident - 2048) / stage_bytes;
+    if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
+    if (stages > k_iters_per_block) stages = k_iters_per_block;
+    return stages < 2 ? 2 : stages;
+}
+
+template <int BN, bool SWAP, typename TOut>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TOut* C, long long split_stride, int ldc,
                      int RA, int RB, int k_iters, int splits, int* err, cudaStream_t s) {
-    const size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
-    auto kern = gemm_tc_kernel<BN, STAGES, SWAP, TOut>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    const int stage_bytes = TC_BM * TC_BK * 2 + BN * TC_BK * 2;
     const int per_split = (k_iters + splits - 1) / splits;
     dim3 grid((RA + TC_BM - 1) / TC_BM, (RB + BN - 1) / BN, splits);
-    kern<<<grid, TC_THREADS, smem, s>>>(ma, mb, C, split_stride, ldc, RA, RB, k_iters, per_split, err);
+    const int stages = pick_stages(stage_bytes, (long long)grid.x * grid.y * grid.z, per_split);
+    const size_t smem = (size_t)stages * stage_bytes + 1024;
+    auto kern = gemm_tc_kernel<BN, SWAP, TOut>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    illm_launch(kern, dim3(grid), dim3(TC_THREADS), smem, s, ma, mb, C, split_stride, ldc, RA, RB, k_iters, per_split, stages, err);
     return illm_launch_status();
+}
+
+extern "C" int illm_gemm_bf16_tc_tune(int stages) {
+    g_tc_stages_override = stages;
+    return 0;
 }
 
 template <typename TOut>
@@ -292,25 +319,25 @@ static int run_tc(const void* X, const void* W, TOut* out, int M, int N, int K, 
         }
         if (splits > 1) {
             const long long n = (long long)M * N;
-            if (bn == 16) rc = launch_tc<16, 4, true, float>(ma, mb, ws, n, N, N, M, k_iters, splits, err, s);
-            else if (bn == 32) rc = launch_tc<32, 4, true, float>(ma, mb, ws, n, N, N, M, k_iters, splits, err, s);
-            else rc = launch_tc<64, 4, true, float>(ma, mb, ws, n, N, N, M, k_iters, splits, err, s);
+            if (bn == 16) rc = launch_tc<16, true, float>(ma, mb, ws, n, N, N, M, k_iters, splits, err, s);
+            else if (bn == 32) rc = launch_tc<32, true, float>(ma, mb, ws, n, N, N, M, k_iters, splits, err, s);
+            else rc = launch_tc<64, true, float>(ma, mb, ws, n, N, N, M, k_iters, splits, err, s);
             if (rc != 0) return rc;
-            splitk_reduce_kernel<TOut><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(ws, out, n, splits);
+            illm_launch(splitk_reduce_kernel<TOut>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, ws, out, n, splits);
             return illm_launch_status();
         }
-        if (bn == 16) return launch_tc<16, 4, true, TOut>(ma, mb, out, 0, N, N, M, k_iters, 1, err, s);
-        if (bn == 32) return launch_tc<32, 4, true, TOut>(ma, mb, out, 0, N, N, M, k_iters, 1, err, s);
-        return launch_tc<64, 4, true, TOut>(ma, mb, out, 0, N, N, M, k_iters, 1, err, s);
+        if (bn == 16) return launch_tc<16, true, TOut>(ma, mb, out, 0, N, N, M, k_iters, 1, err, s);
+        if (bn == 32) return launch_tc<32, true, TOut>(ma, mb, out, 0, N, N, M, k_iters, 1, err, s);
+        return launch_tc<64, true, TOut>(ma, mb, out, 0, N, N, M, k_iters, 1, err, s);
     }
     // prompts: A = X (tokens on the lanes), B = W
     if ((rc = make_map(&ma, X, M, K, TC_BM)) != 0) return rc;
     if (N >= 256) {
         if ((rc = make_map(&mb, W, N, K, 256)) != 0) return rc;
-        return launch_tc<256, 4, false, TOut>(ma, mb, out, 0, N, M, N, k_iters, 1, err, s);
+        return launch_tc<256, false, TOut>(ma, mb, out, 0, N, M, N, k_iters, 1, err, s);
     }
     if ((rc = make_map(&mb, W, N, K, 128)) != 0) return rc;
-    return launch_tc<128, 4, false, TOut>(ma, mb, out, 0, N, M, N, k_iters, 1, err, s);
+    return launch_tc<128, false, TOut>(ma, mb, out, 0, N, M, N, k_iters, 1, err, s);
 }
 
 // out_dtype: ILLM_BF16 or ILLM_F32.  `ws`: float workspace of splits * M * N elements (splits > 1

@@ -18,6 +18,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restri
                                    const TW* __restrict__ w, TA* __restrict__ y,
                                    const int* __restrict__ rows, int H, float eps,
                                    int write_resid) {
+    pdl_grid_sync();
     extern __shared__ float row[];
     __shared__ float scratch[32];
     const int r = rows ? rows[blockIdx.x] : blockIdx.x;
@@ -46,6 +47,7 @@ template <typename TA, typename TW, int ITERS>
 __global__ void __launch_bounds__(RN_THREADS)
 add_rmsnorm_reg_kernel(float* __restrict__ resid, const TA* __restrict__ delta, const TW* __restrict__ w,
                        TA* __restrict__ y, const int* __restrict__ rows, int H, float eps, int write_resid) {
+    pdl_grid_sync();
     __shared__ float scratch[32];
     const int r = rows ? rows[blockIdx.x] : blockIdx.x;
     float* x = resid + (size_t)r * H;
@@ -90,7 +92,7 @@ static int launch(float* resid, const void* delta, const void* w, void* y, const
     if ((H & 7) == 0 && H <= 8 * 8 * RN_THREADS) {
         const int iters = (H / 8 + RN_THREADS - 1) / RN_THREADS;
 #define RN_CASE(N)                                                                                   \
-    add_rmsnorm_reg_kernel<TA, TW, N><<<n_rows, RN_THREADS, 0, s>>>(resid, (const TA*)delta, (const TW*)w, \
+    illm_launch(add_rmsnorm_reg_kernel<TA, TW, N>, dim3(n_rows), dim3(RN_THREADS), 0, s, resid, (const TA*)delta, (const TW*)w, \
                                                                    (TA*)y, rows, H, eps, write_resid)
         if (iters <= 1) RN_CASE(1);
         else if (iters <= 2) RN_CASE(2);
@@ -107,7 +109,7 @@ static int launch(float* resid, const void* delta, const void* w, void* y, const
         if (e != cudaSuccess) return (int)e;
     }
     int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
-    kern<<<n_rows, threads, smem, s>>>(resid, (const TA*)delta, (const TW*)w, (TA*)y, rows, H, eps,
+    illm_launch(kern, dim3(n_rows), dim3(threads), smem, s, resid, (const TA*)delta, (const TW*)w, (TA*)y, rows, H, eps,
                                        write_resid);
     return illm_launch_status();
 }
@@ -131,6 +133,7 @@ extern "C" int illm_add_rmsnorm(float* resid, const void* delta, const void* w, 
 // resid[r] += delta[r] without a norm (flushes a pending addition of the residual stream).
 template <typename TA>
 __global__ void residual_add_kernel(float* __restrict__ resid, const TA* __restrict__ delta, size_t n) {
+    pdl_grid_sync();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) resid[i] += to_f32(delta[i]);
 }
@@ -141,9 +144,9 @@ extern "C" int illm_residual_add(float* resid, const void* delta, int act_dtype,
     cudaStream_t s = (cudaStream_t)stream;
     unsigned blocks = (unsigned)((n + 255) / 256);
     if (act_dtype == ILLM_BF16)
-        residual_add_kernel<bf16><<<blocks, 256, 0, s>>>(resid, (const bf16*)delta, (size_t)n);
+        illm_launch(residual_add_kernel<bf16>, dim3(blocks), dim3(256), 0, s, resid, (const bf16*)delta, (size_t)n);
     else if (act_dtype == ILLM_F32)
-        residual_add_kernel<float><<<blocks, 256, 0, s>>>(resid, (const float*)delta, (size_t)n);
+        illm_launch(residual_add_kernel<float>, dim3(blocks), dim3(256), 0, s, resid, (const float*)delta, (size_t)n);
     else
         return ILLM_ERR_BAD_ARG;
     return illm_launch_status();

@@ -23,6 +23,7 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const float2* __restr
                                      TA* __restrict__ kc, TA* __restrict__ vc, int nh, int nkv, int d,
                                      int rot, int page_size, int write_kv, int table_positions,
                                      int* __restrict__ err) {
+    pdl_grid_sync();
     const int t = blockIdx.x;
     const int p = token_pos[t];
     const int half = rot >> 1;
@@ -116,11 +117,11 @@ extern "C" int illm_rope_kv_write(void* qkv, const float* cos_sin, const int* to
     if (T > 2147483647 / 2 || grid.y > 65535) return ILLM_ERR_BAD_ARG;
     int threads = 32;
     if (act_dtype == ILLM_BF16)
-        rope_kv_write_kernel<bf16><<<grid, threads, 0, s>>>(
+        illm_launch(rope_kv_write_kernel<bf16>, dim3(grid), dim3(threads), 0, s, 
             (bf16*)qkv, (const float2*)cos_sin, token_pos, token_seq, block_table, max_pages,
             (bf16*)kc, (bf16*)vc, nh, nkv, d, rot, page_size, write_kv, table_positions, err);
     else if (act_dtype == ILLM_F32)
-        rope_kv_write_kernel<float><<<grid, threads, 0, s>>>(
+        illm_launch(rope_kv_write_kernel<float>, dim3(grid), dim3(threads), 0, s, 
             (float*)qkv, (const float2*)cos_sin, token_pos, token_seq, block_table, max_pages,
             (float*)kc, (float*)vc, nh, nkv, d, rot, page_size, write_kv, table_positions, err);
     else

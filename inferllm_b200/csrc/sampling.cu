@@ -22,6 +22,7 @@
 #include "common.cuh"
 
 __global__ void argmax_kernel(const float* __restrict__ logits, int V, int ld, int* __restrict__ out) {
+    pdl_grid_sync();
     __shared__ float bv[32];
     __shared__ int bi[32];
     const float* row = logits + (size_t)blockIdx.x * ld;
@@ -55,7 +56,7 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int V, int ld, i
 extern "C" int illm_argmax(const float* logits, int B, int V, int ld, int* out, void* stream) {
     if (B <= 0) return 0;
     if (V <= 0) return ILLM_ERR_BAD_ARG;
-    argmax_kernel<<<B, 512, 0, (cudaStream_t)stream>>>(logits, V, ld, out);
+    illm_launch(argmax_kernel, dim3(B), dim3(512), 0, (cudaStream_t)stream, logits, V, ld, out);
     return illm_launch_status();
 }
 
@@ -72,6 +73,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int V, int ld, float* __restrict__ z_all,
               const int* __restrict__ last_tokens, int n_last, float temp, float penalty, int top_k,
               float top_p, const float* __restrict__ uniforms, int* __restrict__ out) {
+    pdl_grid_sync();
     __shared__ float scratch[32];
     __shared__ float partial[SAMPLE_THREADS];
     __shared__ int chosen;
@@ -193,7 +195,7 @@ extern "C" int illm_sample(const float* logits, int B, int V, int ld, float* z_s
                            float top_p, const float* uniforms, int* out, void* stream) {
     if (B <= 0) return 0;
     if (V <= 0 || !(temp > 0.f) || !(penalty > 0.f)) return ILLM_ERR_BAD_ARG;
-    sample_kernel<<<B, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(
+    illm_launch(sample_kernel, dim3(B), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, 
         logits, V, ld, z_scratch, last_tokens, n_last, temp, penalty, top_k, top_p, uniforms, out);
     return illm_launch_status();
 }

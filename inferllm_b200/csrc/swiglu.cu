@@ -6,6 +6,7 @@
 
 template <typename TA>
 __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I) {
+    pdl_grid_sync();
     const int t = blockIdx.y;
     const TA* g = gu + (size_t)t * 2 * I;
     const TA* u = g + I;
@@ -21,6 +22,7 @@ __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, i
 // 8 elements per thread with 16-byte loads (I a multiple of 8).
 template <typename TA>
 __global__ void swiglu_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, long long n_vec) {
+    pdl_grid_sync();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_vec) return;
     const int per_row = I / 8;
@@ -43,9 +45,9 @@ extern "C" int illm_swiglu(const void* gu, void* out, int act_dtype, int T, int 
         const long long n_vec = (long long)T * (I / 8);
         const unsigned blocks = (unsigned)((n_vec + 255) / 256);
         if (act_dtype == ILLM_BF16)
-            swiglu_vec_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)gu, (bf16*)out, I, n_vec);
+            illm_launch(swiglu_vec_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)gu, (bf16*)out, I, n_vec);
         else if (act_dtype == ILLM_F32)
-            swiglu_vec_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, (float*)out, I, n_vec);
+            illm_launch(swiglu_vec_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)gu, (float*)out, I, n_vec);
         else
             return ILLM_ERR_BAD_ARG;
         return illm_launch_status();
@@ -55,10 +57,10 @@ extern "C" int illm_swiglu(const void* gu, void* out, int act_dtype, int T, int 
         int n = T - t0 < 65535 ? T - t0 : 65535;
         dim3 grid((I + 255) / 256 > 64 ? 64 : (I + 255) / 256, n);
         if (act_dtype == ILLM_BF16)
-            swiglu_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)gu + (size_t)t0 * 2 * I,
+            illm_launch(swiglu_kernel<bf16>, dim3(grid), dim3(256), 0, s, (const bf16*)gu + (size_t)t0 * 2 * I,
                                                      (bf16*)out + (size_t)t0 * I, I);
         else if (act_dtype == ILLM_F32)
-            swiglu_kernel<float><<<grid, 256, 0, s>>>((const float*)gu + (size_t)t0 * 2 * I,
+            illm_launch(swiglu_kernel<float>, dim3(grid), dim3(256), 0, s, (const float*)gu + (size_t)t0 * 2 * I,
                                                       (float*)out + (size_t)t0 * I, I);
         else
             return ILLM_ERR_BAD_ARG;

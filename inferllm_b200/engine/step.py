@@ -41,6 +41,7 @@ class EngineOptions:
     max_batch: Optional[int] = None     # slots; default max_tokens / page_size
     page_size: int = 64
     cuda_graphs: bool = True       # replay one-token-per-sequence steps from captured CUDA graphs
+    gemm: str = "auto"             # bfloat16 products: "auto" | "tc" | "library" (see kernels.ops.set_gemm_backend)
 
 
 @dataclass
@@ -144,6 +145,7 @@ class Engine:
             raise EngineError("inferllm_b200 needs a CUDA device: there is no CPU path")
         from ..kernels.lib import load
         load()  # fail here, loudly, if the kernels cannot be built or loaded
+        ops.set_gemm_backend(options.gemm)
         dev = torch.device("cuda", options.device_id)
         torch.cuda.set_device(dev)
         return Runtime(dev, _DTYPES[options.dtype], options.page_size)
@@ -262,6 +264,10 @@ class Engine:
     def check_device_errors(self) -> None:
         """Read the kernels' error word (synchronises)."""
         code = int(self.err.item())
+        tc = ops.tc_error_word(self.rt.device)
+        if int(tc.item()):
+            tc.zero_()
+            raise EngineError("a wait inside the tensor-core matrix product timed out")
         if code:
             self.err.zero_()
             what = {1: "a token id outside the embedding table", 2: "a cache write to a page that "

@@ -25,6 +25,8 @@ _SIGNATURES = {
     "illm_attention_decode_supported": [I, I, I],
     "illm_attention_prefill": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],
     "illm_gemm_bf16_tc": [P, P, P, I, I, I, I, P, I, P, P],
+    "illm_gemm_bf16_tc_tune": [I],
+    "illm_set_pdl": [I],
     "illm_gemm_f32_nt": [P, P, P, I, I, I, I, I, I, P],
     "illm_argmax": [P, I, I, I, P, P],
     "illm_sample": [P, I, I, I, P, P, I, F, F, I, F, P, P, P],

@@ -281,7 +281,7 @@ def gemm_tc_splits(M, N, K):
     return max(1, min(2 * N_SMS // tiles, k_iters // 8))
 
 
-def gemm_bf16_tc(x, w, out_dtype=torch.bfloat16):
+def gemm_bf16_tc(x, w, out_dtype=torch.bfloat16, splits=None):
     """bfloat16 x [M, K] . w [N, K]^T on tcgen05 tensor cores, float32 accumulation."""
     _need(x, "x", torch.bfloat16, 2)
     _need(w, "w", torch.bfloat16, 2)
@@ -292,22 +292,31 @@ def gemm_bf16_tc(x, w, out_dtype=torch.bfloat16):
     if K % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
         raise KernelError(f"gemm_bf16_tc: K = {K} must be a multiple of 8 and the operands 16-byte aligned")
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    splits = gemm_tc_splits(M, N, K)
+    if splits is None:
+        splits = gemm_tc_splits(M, N, K)
     ws = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
     _check(load().illm_gemm_bf16_tc(_ptr(x), _ptr(w), _ptr(out), act_code(out_dtype), M, N, K, _ptr(ws),
                                     splits, _ptr(tc_error_word(x.device)), _stream()), "gemm_bf16_tc")
     return out
 
 
-_GEMM_BACKEND = "library"
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch of the package's kernels (on by default)."""
+    load().illm_set_pdl(1 if on else 0)
+
+
+_GEMM_BACKEND = "auto"
+GEMM_TC_MAX_TOKENS_AUTO = 64
 
 
 def set_gemm_backend(name: str) -> None:
-    """"tc": the package's tcgen05 kernel for every bfloat16 product it can take; "library":
-    cuBLAS through torch.mm."""
+    """Which kernel runs the bfloat16 matrix products.  "tc": the package's tcgen05 kernel for
+    every product it can take (K a multiple of 8); "library": cuBLAS through torch.mm; "auto"
+    (default): the tcgen05 kernel for decode-sized products (at most 64 tokens), where it
+    streams the weights in its swapped, split-K form, and the library for larger ones."""
     global _GEMM_BACKEND
-    if name not in ("tc", "library"):
-        raise ValueError("gemm backend must be 'tc' or 'library'")
+    if name not in ("tc", "library", "auto"):
+        raise ValueError("gemm backend must be 'tc', 'library' or 'auto'")
     _GEMM_BACKEND = name
 
 
@@ -318,7 +327,9 @@ def linear(x, w, out_dtype=None):
         return gemm_f32(x, w)
     _need(x, "x", torch.bfloat16, 2)
     _need(w, "w", torch.bfloat16, 2)
-    if _GEMM_BACKEND == "tc" and x.shape[1] % 8 == 0 and x.shape[0] > 0:
+    M, K = x.shape
+    if M > 0 and K % 8 == 0 and (_GEMM_BACKEND == "tc" or (
+            _GEMM_BACKEND == "auto" and M <= GEMM_TC_MAX_TOKENS_AUTO)):
         return gemm_bf16_tc(x, w, out_dtype or torch.bfloat16)
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
