@@ -6,7 +6,7 @@
 // key or value is fetched once however many query heads share it (the reference's only grouped
 // attention loops over the query heads and re-reads K and V for each,
 // src/kern/gpu/kernel_gpu.cu:688-756).  Inside a block every key row is read by D/8 neighbouring
-// lanes with one 16-byte load each (fully coalesced), four keys per lane group in flight, and
+// lanes with one 16-byte load each (fully coalesced), eight keys per lane group in flight, and
 // each lane group keeps a running maximum, sum and weighted value sum of its own (scores and
 // softmax in float32; formulas src/kern/naive/naive.cpp:606-632, :531-553, :209-240, :664-691).
 // Partial results go to a scratch buffer [token, head, chunk] and a second kernel merges the
@@ -20,7 +20,24 @@
 
 #define AD_THREADS 128
 #define AD_CHUNK 256   // keys per block
-#define AD_U 4         // keys per lane group and iteration
+#define AD_U 8         // keys per lane group and iteration
+
+// 16-byte load that does not linger in L1 (every key and value is used once per step)
+__device__ __forceinline__ uint4 ld_stream16(const bf16* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 t = __bfloat1622float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
 
 template <int D, int G>
 __global__ void __launch_bounds__(AD_THREADS)
@@ -64,53 +81,62 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
         const int base = base0 + grp * AD_U;
         const int page = base <= last ? bt[base / page_size] : 0;
         const size_t row0 = (((size_t)page * nkv + hk) * page_size + (base % page_size)) * D + sub * 8;
-        float kf[AD_U][8], vf[AD_U][8];
+        // all loads of the stretch are issued before anything is computed: 2 * AD_U 16-byte loads
+        // in flight per thread, kept as raw bits until they are used
+        uint4 kraw[AD_U], vraw[AD_U];
         bool ok[AD_U];
 #pragma unroll
         for (int u = 0; u < AD_U; u++) {
             ok[u] = (base + u >= first) && (base + u <= last);
+            kraw[u] = make_uint4(0u, 0u, 0u, 0u);
+            vraw[u] = make_uint4(0u, 0u, 0u, 0u);
             if (ok[u]) {
-                load8(kc + row0 + (size_t)u * D, kf[u]);
-                load8(vc + row0 + (size_t)u * D, vf[u]);
+                kraw[u] = ld_stream16(kc + row0 + (size_t)u * D);
+                vraw[u] = ld_stream16(vc + row0 + (size_t)u * D);
             }
         }
         float s[G][AD_U];
 #pragma unroll
-        for (int g = 0; g < G; g++)
+        for (int u = 0; u < AD_U; u++) {
+            float kf[8];
+            unpack8(kraw[u], kf);
 #pragma unroll
-            for (int u = 0; u < AD_U; u++) {
+            for (int g = 0; g < G; g++) {
                 float d = 0.f;
-                if (ok[u]) {
 #pragma unroll
-                    for (int i = 0; i < 8; i++) d = fmaf(qr[g][i], kf[u][i], d);
-                }
+                for (int i = 0; i < 8; i++) d = fmaf(qr[g][i], kf[i], d);
 #pragma unroll
                 for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
                 s[g][u] = ok[u] ? d * scale_log2e : -INFINITY;
             }
+        }
+        float pe[G][AD_U];
 #pragma unroll
         for (int g = 0; g < G; g++) {
             float mn = m[g];
 #pragma unroll
             for (int u = 0; u < AD_U; u++) mn = fmaxf(mn, s[g][u]);
-            if (mn == -INFINITY) continue;   // no valid key in this stretch for this group
-            const float corr = exp2f(m[g] - mn);  // m = -inf gives 0
-            float pe[AD_U], ps = 0.f;
+            const float mu = (mn == -INFINITY) ? 0.f : mn;      // nothing valid yet: all weights 0
+            const float corr = exp2f(m[g] - mu);                // m = -inf gives 0
+            float ps = 0.f;
 #pragma unroll
             for (int u = 0; u < AD_U; u++) {
-                pe[u] = exp2f(s[g][u] - mn);
-                ps += pe[u];
+                pe[g][u] = exp2f(s[g][u] - mu);
+                ps += pe[g][u];
             }
             l[g] = l[g] * corr + ps;
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                float a = acc[g][i] * corr;
-#pragma unroll
-                for (int u = 0; u < AD_U; u++)
-                    if (ok[u]) a = fmaf(pe[u], vf[u][i], a);
-                acc[g][i] = a;
-            }
+            for (int i = 0; i < 8; i++) acc[g][i] *= corr;
             m[g] = mn;
+        }
+#pragma unroll
+        for (int u = 0; u < AD_U; u++) {
+            float vf[8];
+            unpack8(vraw[u], vf);
+#pragma unroll
+            for (int g = 0; g < G; g++)
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc[g][i] = fmaf(pe[g][u], vf[i], acc[g][i]);
         }
     }
 

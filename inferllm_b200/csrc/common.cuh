@@ -75,14 +75,16 @@ __device__ __forceinline__ void store8(float* p, const float* f) {
 }
 
 // Programmatic dependent launch.  Every kernel of the package starts with pdl_grid_sync(): it
-// waits until the kernels before it in the stream have finished and their writes are visible,
-// then lets the kernel after it begin to launch.  With the launch attribute below, a kernel's
-// blocks are therefore set up (scheduling, shared memory, barriers) while its predecessor is still
-// draining, which hides most of the gap between the many short kernels of a decode step.
-// Without the attribute both instructions do nothing.
+// lets the kernel after it in the stream begin to launch, then waits until the kernels before
+// it have finished and their writes are visible.  With the launch attribute below, a kernel's
+// blocks are therefore scheduled and set up (shared memory, barriers, and in the matrix product
+// the first weight tiles) while its predecessors are still running, which hides most of the gap
+// between the many short kernels of a decode step.  A kernel still touches no activation before
+// its own wait, and a kernel's wait covers everything before it in the stream, so the order of
+// reads and writes is the stream's.  Without the attribute both instructions do nothing.
 __device__ __forceinline__ void pdl_grid_sync() {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 inline int g_illm_pdl = 1;   // illm_set_pdl() switches the launch attribute off (e.g. for profilers)

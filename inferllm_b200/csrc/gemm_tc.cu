@@ -148,16 +148,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = tmem_holder;
-    // everything above (barriers, tensor memory) was set up while the previous kernel drained;
-    // from here on global memory is touched
-    pdl_grid_sync();
+    // Everything above (barriers, tensor memory) was set up while the previous kernel drained, and
+    // the kernel after this one may begin its own set-up now.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         if (lane == 0) {
+            // The weights never depend on an earlier kernel: the first ring of weight tiles is
+            // requested before waiting for the previous kernel, so that the memory system is
+            // already streaming when the activations become valid.
+            const int n_pre = n_k < STAGES ? n_k : STAGES;
+            for (int i = 0; i < n_pre; i++) {
+                mbar_expect_tx(full0 + 8 * i, A_BYTES + B_BYTES);
+                const int kx = (k_begin + i) * TC_BK;
+                if (SWAP) tma_load_2d(a_base + i * A_BYTES, &map_a, kx, ra0, full0 + 8 * i);
+                else tma_load_2d(b_base + i * B_BYTES, &map_b, kx, rb0, full0 + 8 * i);
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (int i = 0; i < n_pre; i++) {
+                const int kx = (k_begin + i) * TC_BK;
+                if (SWAP) tma_load_2d(b_base + i * B_BYTES, &map_b, kx, rb0, full0 + 8 * i);
+                else tma_load_2d(a_base + i * A_BYTES, &map_a, kx, ra0, full0 + 8 * i);
+            }
             bool alive = true;
-            for (int i = 0; i < n_k && alive; i++) {
+            for (int i = n_pre; i < n_k && alive; i++) {
                 const int s = i % STAGES;
-                if (i >= STAGES) alive = mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, err);
+                alive = mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, err);
                 if (!alive) break;
                 mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
                 const int kx = (k_begin + i) * TC_BK;
@@ -186,6 +202,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else {
         // epilogue: warp w may touch the 32 lanes of tensor memory of its quadrant w % 4
         const int quad = warp & 3;
+        asm volatile("griddepcontrol.wait;" ::: "memory");   // before any store: the output may alias
         const bool ok = mbar_wait(done_bar, 0, err);
         tc_fence_after();
         const int ra = ra0 + quad * 32 + lane;

@@ -234,7 +234,7 @@ def test_attention_generic(dtype, nh, nkv, d, page, window):
 
 @pytest.mark.parametrize("nh,nkv,d,page,window", [
     (4, 4, 128, 64, None), (8, 2, 128, 16, None), (8, 1, 128, 64, None), (6, 2, 64, 8, None),
-    (3, 3, 64, 64, None), (16, 2, 64, 32, None), (4, 2, 128, 64, 300), (2, 1, 64, 4, 5)])
+    (3, 3, 64, 64, None), (16, 2, 64, 32, None), (4, 2, 128, 64, 300), (2, 1, 64, 8, 5)])
 def test_attention_decode(nh, nkv, d, page, window):
     """The split-key decode kernel: sequences that end inside the first chunk, exactly on a chunk
     border, and several chunks long."""
@@ -321,7 +321,7 @@ def test_attention_decode_says_what_it_takes():
     assert not ops.attention_decode_supported(torch.float32, 4, 4, 128, 64)
     assert not ops.attention_decode_supported(torch.bfloat16, 4, 4, 24, 64)
     assert not ops.attention_decode_supported(torch.bfloat16, 5, 1, 128, 64)
-    assert not ops.attention_decode_supported(torch.bfloat16, 4, 4, 128, 6)
+    assert not ops.attention_decode_supported(torch.bfloat16, 4, 4, 128, 12)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
