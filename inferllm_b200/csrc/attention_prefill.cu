@@ -1,9 +1,10 @@
 // Causal attention of whole prompts over the paged cache, bfloat16, on the tensor cores.
 //
-// Flash-attention style: the score matrix is never written out.  A block owns 64 consecutive
+// Flash-attention style: the score matrix is never written out.  A block owns 128 consecutive
 // query tokens of one (sequence, head) and walks the keys of that sequence in blocks of 64, from
 // the cache pages into shared memory (cp.async, double buffered, XOR-swizzled rows so that
-// ldmatrix is conflict-free); each of its 4 warps holds 16 query rows: S = Q K^T and O += P V are
+// ldmatrix is conflict-free); each of its 4 warps holds 32 query rows, so that every K or V
+// fragment it fetches from shared memory feeds two MMAs: S = Q K^T and O += P V are
 // m16n8k16 bfloat16 MMAs with float32 accumulators, and the running maximum, the sum and the
 // exponentials are float32 (exp2 on scores pre-multiplied by log2 e).  P is rounded to bfloat16
 // for the second product.  This replaces the reference's four launches over a materialised
@@ -21,7 +22,6 @@
 
 #include "common.cuh"
 
-#define FA_BM 64
 #define FA_BN 64
 #define FA_THREADS 128
 
@@ -56,7 +56,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 // element offset of 16-byte chunk `c` of row `r` in a [rows][D] bfloat16 tile with swizzled chunks
 template <int D> __device__ __forceinline__ int swz(int r, int c) { return r * D + ((c ^ (r & 7)) << 3); }
 
-template <int D>
+template <int D, int MT>
 __global__ void __launch_bounds__(FA_THREADS)
 attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kc,
                          const bf16* __restrict__ vc, const int* __restrict__ block_table, int max_pages,
@@ -64,21 +64,23 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
                          bf16* __restrict__ out, int nh, int nkv, int page_size, int window,
                          float scale_log2e) {
     pdl_grid_sync();
-    constexpr int CH = D / 8;       // 16-byte chunks per row
-    constexpr int KS = D / 16;      // k-steps of Q K^T
-    constexpr int NT_D = D / 8;     // n-tiles of the output
+    constexpr int BM = 4 * MT * 16;   // query rows of the block: MT m-tiles of 16 rows per warp
+    constexpr int CH = D / 8;         // 16-byte chunks per row
+    constexpr int KS = D / 16;        // k-steps of Q K^T
+    constexpr int NT_D = D / 8;       // n-tiles of the output
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
-    bf16* Ks = Qs + FA_BM * D;              // [2][FA_BN][D]
+    bf16* Ks = Qs + BM * D;                 // [2][FA_BN][D]
     bf16* Vs = Ks + 2 * FA_BN * D;          // [2][FA_BN][D]
 
-    const int b = blockIdx.z, h = blockIdx.y, tile = blockIdx.x;
+    // the last tiles of a prompt see the most keys: they are started first
+    const int b = blockIdx.z, h = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
     const int q0 = cu_q[b], qlen = cu_q[b + 1] - q0;
-    const int row0 = tile * FA_BM;
+    const int row0 = tile * BM;
     if (row0 >= qlen) return;
     const int total = seq_lens[b], past = total - qlen;
     const int hk = h / (nh / nkv);
-    const int rows_here = (qlen - row0 < FA_BM) ? qlen - row0 : FA_BM;
+    const int rows_here = (qlen - row0 < BM) ? qlen - row0 : BM;
     const int first_pos = past + row0, last_pos = first_pos + rows_here - 1;
     const int lo_key = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
     const int jb0 = lo_key / FA_BN, jb1 = last_pos / FA_BN;
@@ -86,9 +88,11 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
+    const int mtx = lane >> 3;          // which 8x8 matrix of an ldmatrix.x4 this lane addresses
+    const int wrow0 = warp * MT * 16;   // first row of this warp inside the tile
 
     // ---- Q tile -> shared (zero rows beyond the sequence's tokens)
-    for (int i = tid; i < FA_BM * CH; i += FA_THREADS) {
+    for (int i = tid; i < BM * CH; i += FA_THREADS) {
         const int r = i / CH, c = i % CH;
         const bool ok = r < rows_here;
         const bf16* src = ok ? q + (size_t)(q0 + row0 + r) * q_stride + (size_t)h * D + c * 8 : q;
@@ -113,19 +117,25 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
     load_kv(jb0, 0);
     cp_async_commit();
 
-    // ---- per-warp state: 16 query rows; this thread owns rows g and g+8 of them
-    float o[NT_D][4];
+    // ---- per-warp state: MT x 16 query rows; this thread owns rows g and g+8 of each m-tile
+    float o[MT][NT_D][4];
+    float m_run[MT][2], l_run[MT][2];
+    int pos_r[MT][2];
 #pragma unroll
-    for (int i = 0; i < NT_D; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-    int pos_r[2];
+    for (int mt = 0; mt < MT; mt++) {
 #pragma unroll
-    for (int e = 0; e < 2; e++) {
-        const int r = warp * 16 + g + e * 8;
-        pos_r[e] = (r < rows_here) ? first_pos + r : last_pos;
+        for (int i = 0; i < NT_D; i++) o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            m_run[mt][e] = -INFINITY;
+            l_run[mt][e] = 0.f;
+            const int r = wrow0 + mt * 16 + g + e * 8;
+            pos_r[mt][e] = (r < rows_here) ? first_pos + r : last_pos;
+        }
     }
-    unsigned qf[KS][4];
-    bool q_loaded = false;
+    // a warp whose rows all lie beyond the prompt has nothing to compute (it still helps loading)
+    const bool warp_active = wrow0 < rows_here;
+    const int warp_last_pos = (wrow0 + MT * 16 - 1 < rows_here) ? first_pos + wrow0 + MT * 16 - 1 : last_pos;
 
     for (int jb = jb0; jb <= jb1; jb++) {
         const int buf = (jb - jb0) & 1;
@@ -133,93 +143,101 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        if (!q_loaded) {
-#pragma unroll
-            for (int ks = 0; ks < KS; ks++) {
-                const int mtx = lane >> 3;
-                const int r = warp * 16 + (mtx & 1) * 8 + (lane & 7);
-                ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], smem_u32(Qs + swz<D>(r, ks * 2 + (mtx >> 1))));
-            }
-            q_loaded = true;
-        }
         const bf16* kb = Ks + buf * FA_BN * D;
         const bf16* vb = Vs + buf * FA_BN * D;
-
-        // S = Q K^T : 16 x 64 per warp, 8 n-tiles
-        float s[FA_BN / 8][4];
-#pragma unroll
-        for (int i = 0; i < FA_BN / 8; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-#pragma unroll
-        for (int ks = 0; ks < KS; ks++) {
-#pragma unroll
-            for (int np = 0; np < FA_BN / 16; np++) {
-                const int mtx = lane >> 3;
-                const int r = np * 16 + (mtx >> 1) * 8 + (lane & 7);
-                unsigned b0, b1, b2, b3;
-                ldmatrix_x4(b0, b1, b2, b3, smem_u32(kb + swz<D>(r, ks * 2 + (mtx & 1))));
-                mma_bf16(s[np * 2], qf[ks], b0, b1);
-                mma_bf16(s[np * 2 + 1], qf[ks], b2, b3);
-            }
-        }
-
-        // scale, mask, running maximum
         const int key0 = jb * FA_BN;
-        const bool need_mask = (key0 + FA_BN - 1 > first_pos) || (window > 0);
-        float m_new[2] = {m_run[0], m_run[1]};
+        // keys of this block all lie after the warp's last row: nothing to add for this warp
+        if (warp_active && key0 <= warp_last_pos) {
+            // S = Q K^T : (MT x 16) x 64 per warp
+            float s[MT][FA_BN / 8][4];
 #pragma unroll
-        for (int nt = 0; nt < FA_BN / 8; nt++) {
+            for (int mt = 0; mt < MT; mt++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                float v = s[nt][e] * scale_log2e;
-                if (need_mask) {
-                    const int key = key0 + nt * 8 + t4 * 2 + (e & 1);
-                    const int pr = pos_r[e >> 1];
-                    if (key > pr || (window > 0 && key < pr - window + 1)) v = -INFINITY;
+                for (int i = 0; i < FA_BN / 8; i++) s[mt][i][0] = s[mt][i][1] = s[mt][i][2] = s[mt][i][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                unsigned qf[MT][4];
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    const int r = wrow0 + mt * 16 + (mtx & 1) * 8 + (lane & 7);
+                    ldmatrix_x4(qf[mt][0], qf[mt][1], qf[mt][2], qf[mt][3],
+                                smem_u32(Qs + swz<D>(r, ks * 2 + (mtx >> 1))));
                 }
-                s[nt][e] = v;
-                m_new[e >> 1] = fmaxf(m_new[e >> 1], v);
+#pragma unroll
+                for (int np = 0; np < FA_BN / 16; np++) {
+                    const int r = np * 16 + (mtx >> 1) * 8 + (lane & 7);
+                    unsigned b0, b1, b2, b3;
+                    ldmatrix_x4(b0, b1, b2, b3, smem_u32(kb + swz<D>(r, ks * 2 + (mtx & 1))));
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++) {
+                        mma_bf16(s[mt][np * 2], qf[mt], b0, b1);
+                        mma_bf16(s[mt][np * 2 + 1], qf[mt], b2, b3);
+                    }
+                }
             }
-        }
-        float corr[2], m_use[2], psum[2] = {0.f, 0.f};
+
+            // scale, mask, running maximum; P = exp2(S - m) packed as A fragments
+            const bool need_mask = (key0 + FA_BN - 1 > first_pos + wrow0) || (window > 0);
+            unsigned pf[MT][FA_BN / 16][4];
 #pragma unroll
-        for (int e = 0; e < 2; e++) {
-            m_new[e] = fmaxf(m_new[e], __shfl_xor_sync(0xffffffffu, m_new[e], 1));
-            m_new[e] = fmaxf(m_new[e], __shfl_xor_sync(0xffffffffu, m_new[e], 2));
-            m_use[e] = (m_new[e] == -INFINITY) ? 0.f : m_new[e];
-            corr[e] = (m_run[e] == -INFINITY) ? 0.f : exp2f(m_run[e] - m_use[e]);
-            m_run[e] = m_new[e];
-        }
-        // P = exp2(S - m), packed as A fragments of the second product
-        unsigned pf[FA_BN / 16][4];
+            for (int mt = 0; mt < MT; mt++) {
+                float m_new[2] = {m_run[mt][0], m_run[mt][1]};
 #pragma unroll
-        for (int nt = 0; nt < FA_BN / 8; nt++) {
-            const float p0 = exp2f(s[nt][0] - m_use[0]), p1 = exp2f(s[nt][1] - m_use[0]);
-            const float p2 = exp2f(s[nt][2] - m_use[1]), p3 = exp2f(s[nt][3] - m_use[1]);
-            psum[0] += p0 + p1;
-            psum[1] += p2 + p3;
-            pf[nt >> 1][(nt & 1) * 2] = pack_bf16(p0, p1);
-            pf[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
-        }
+                for (int nt = 0; nt < FA_BN / 8; nt++) {
 #pragma unroll
-        for (int e = 0; e < 2; e++) l_run[e] = l_run[e] * corr[e] + psum[e];
+                    for (int e = 0; e < 4; e++) {
+                        float v = s[mt][nt][e] * scale_log2e;
+                        if (need_mask) {
+                            const int key = key0 + nt * 8 + t4 * 2 + (e & 1);
+                            const int pr = pos_r[mt][e >> 1];
+                            if (key > pr || (window > 0 && key < pr - window + 1)) v = -INFINITY;
+                        }
+                        s[mt][nt][e] = v;
+                        m_new[e >> 1] = fmaxf(m_new[e >> 1], v);
+                    }
+                }
+                float corr[2], m_use[2], psum[2] = {0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < NT_D; i++) {
-            o[i][0] *= corr[0];
-            o[i][1] *= corr[0];
-            o[i][2] *= corr[1];
-            o[i][3] *= corr[1];
-        }
-        // O += P V
+                for (int e = 0; e < 2; e++) {
+                    m_new[e] = fmaxf(m_new[e], __shfl_xor_sync(0xffffffffu, m_new[e], 1));
+                    m_new[e] = fmaxf(m_new[e], __shfl_xor_sync(0xffffffffu, m_new[e], 2));
+                    m_use[e] = (m_new[e] == -INFINITY) ? 0.f : m_new[e];
+                    corr[e] = (m_run[mt][e] == -INFINITY) ? 0.f : fast_exp2(m_run[mt][e] - m_use[e]);
+                    m_run[mt][e] = m_new[e];
+                }
 #pragma unroll
-        for (int ks = 0; ks < FA_BN / 16; ks++) {
+                for (int nt = 0; nt < FA_BN / 8; nt++) {
+                    const float p0 = fast_exp2(s[mt][nt][0] - m_use[0]), p1 = fast_exp2(s[mt][nt][1] - m_use[0]);
+                    const float p2 = fast_exp2(s[mt][nt][2] - m_use[1]), p3 = fast_exp2(s[mt][nt][3] - m_use[1]);
+                    psum[0] += p0 + p1;
+                    psum[1] += p2 + p3;
+                    pf[mt][nt >> 1][(nt & 1) * 2] = pack_bf16(p0, p1);
+                    pf[mt][nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+                }
 #pragma unroll
-            for (int np = 0; np < NT_D / 2; np++) {
-                const int mtx = lane >> 3;
-                const int r = ks * 16 + (mtx & 1) * 8 + (lane & 7);
-                unsigned b0, b1, b2, b3;
-                ldmatrix_x4_trans(b0, b1, b2, b3, smem_u32(vb + swz<D>(r, np * 2 + (mtx >> 1))));
-                mma_bf16(o[np * 2], pf[ks], b0, b1);
-                mma_bf16(o[np * 2 + 1], pf[ks], b2, b3);
+                for (int e = 0; e < 2; e++) l_run[mt][e] = l_run[mt][e] * corr[e] + psum[e];
+#pragma unroll
+                for (int i = 0; i < NT_D; i++) {
+                    o[mt][i][0] *= corr[0];
+                    o[mt][i][1] *= corr[0];
+                    o[mt][i][2] *= corr[1];
+                    o[mt][i][3] *= corr[1];
+                }
+            }
+            // O += P V
+#pragma unroll
+            for (int ks = 0; ks < FA_BN / 16; ks++) {
+#pragma unroll
+                for (int np = 0; np < NT_D / 2; np++) {
+                    const int r = ks * 16 + (mtx & 1) * 8 + (lane & 7);
+                    unsigned b0, b1, b2, b3;
+                    ldmatrix_x4_trans(b0, b1, b2, b3, smem_u32(vb + swz<D>(r, np * 2 + (mtx >> 1))));
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++) {
+                        mma_bf16(o[mt][np * 2], pf[mt][ks], b0, b1);
+                        mma_bf16(o[mt][np * 2 + 1], pf[mt][ks], b2, b3);
+                    }
+                }
             }
         }
         __syncthreads();   // everyone is done with this buffer before the next load overwrites it
@@ -228,20 +246,21 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
 
     // ---- normalise and store
 #pragma unroll
-    for (int e = 0; e < 2; e++) {
-        l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 1);
-        l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 2);
-    }
+    for (int mt = 0; mt < MT; mt++) {
 #pragma unroll
-    for (int e = 0; e < 2; e++) {
-        const int r = warp * 16 + g + e * 8;
-        if (r >= rows_here) continue;
-        const float inv = 1.0f / l_run[e];
-        bf16* dst = out + ((size_t)(q0 + row0 + r) * nh + h) * D;
+        for (int e = 0; e < 2; e++) {
+            float lsum = l_run[mt][e];
+            lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
+            lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
+            const int r = wrow0 + mt * 16 + g + e * 8;
+            if (r >= rows_here) continue;
+            const float inv = 1.0f / lsum;
+            bf16* dst = out + ((size_t)(q0 + row0 + r) * nh + h) * D;
 #pragma unroll
-        for (int i = 0; i < NT_D; i++) {
-            __nv_bfloat162 v = __floats2bfloat162_rn(o[i][e * 2] * inv, o[i][e * 2 + 1] * inv);
-            *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + t4 * 2) = v;
+            for (int i = 0; i < NT_D; i++) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(o[mt][i][e * 2] * inv, o[mt][i][e * 2 + 1] * inv);
+                *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + t4 * 2) = v;
+            }
         }
     }
 }
@@ -250,13 +269,15 @@ template <int D>
 static int launch(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table,
                   int max_pages, const int* cu_q, const int* seq_lens, void* out, int B, int max_q, int nh,
                   int nkv, int page_size, int window, float scale, cudaStream_t s) {
-    const size_t smem = (size_t)(FA_BM + 4 * FA_BN) * D * sizeof(bf16);
-    auto kern = attention_prefill_kernel<D>;
+    constexpr int MT = 2;
+    constexpr int BM = 4 * MT * 16;
+    const size_t smem = (size_t)(BM + 4 * FA_BN) * D * sizeof(bf16);
+    auto kern = attention_prefill_kernel<D, MT>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    dim3 grid((max_q + FA_BM - 1) / FA_BM, nh, B);
+    dim3 grid((max_q + BM - 1) / BM, nh, B);
     illm_launch(kern, dim3(grid), dim3(FA_THREADS), smem, s, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, block_table,
                                         max_pages, cu_q, seq_lens, (bf16*)out, nh, nkv, page_size, window,
                                         scale * 1.4426950408889634f);

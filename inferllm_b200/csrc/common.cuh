@@ -74,6 +74,14 @@ __device__ __forceinline__ void store8(float* p, const float* f) {
     *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
 }
 
+// 2^x by the special-function unit (one instruction, relative error about 2^-22, -inf gives 0):
+// for softmax weights that are rounded to bfloat16 or summed in float32 afterwards.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Programmatic dependent launch.  Every kernel of the package starts with pdl_grid_sync(): it
 // lets the kernel after it in the stream begin to launch, then waits until the kernels before
 // it have finished and their writes are visible.  With the launch attribute below, a kernel's

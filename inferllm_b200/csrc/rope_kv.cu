@@ -13,7 +13,9 @@
 // leaves the cache alone (a layer that reads another layer's keys and values).
 #include "common.cuh"
 
-#define RK_SLOTS_PER_BLOCK 4   // one warp per block, one head slot after the other
+#define RK_WARPS 4
+#define RK_SLOTS_PER_WARP 4
+#define RK_SLOTS_PER_BLOCK (RK_WARPS * RK_SLOTS_PER_WARP)   // each warp takes its head slots one after the other
 
 template <typename TA>
 __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const float2* __restrict__ cs,
@@ -48,8 +50,9 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const float2* __restr
     const size_t head_stride = (size_t)page_size * d;  // between kv heads inside a page
     // this block's share of the head slots: [q heads | k heads | v heads]
     const int n_slots = nh + 2 * nkv;
-    const int s0 = blockIdx.y * RK_SLOTS_PER_BLOCK;
-    const int s1 = min(n_slots, s0 + RK_SLOTS_PER_BLOCK);
+    const int lane = threadIdx.x & 31;
+    const int s0 = blockIdx.y * RK_SLOTS_PER_BLOCK + (threadIdx.x >> 5) * RK_SLOTS_PER_WARP;
+    const int s1 = min(n_slots, s0 + RK_SLOTS_PER_WARP);
     const float2* cst = cs + (size_t)p * half;
     const int rest = d - rot;
     // 8 channels per thread with 16-byte accesses where the sizes allow it
@@ -61,7 +64,7 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const float2* __restr
             if (is_k && !write_kv) continue;
             TA* dst = is_k ? kdst + (size_t)(slot - nh) * head_stride : src;
             if (vec) {
-                for (int j = threadIdx.x * 8; j < half; j += blockDim.x * 8) {
+                for (int j = lane * 8; j < half; j += 32 * 8) {
                     float a[8], b[8], ra[8], rb[8];
                     load8(src + j, a);
                     load8(src + j + half, b);
@@ -75,31 +78,31 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const float2* __restr
                     store8(dst + j + half, rb);
                 }
                 if (is_k)
-                    for (int c = rot + threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+                    for (int c = rot + lane * 8; c < d; c += 32 * 8) {
                         float a[8];
                         load8(src + c, a);
                         store8(dst + c, a);
                     }
             } else {
-                for (int j = threadIdx.x; j < half; j += blockDim.x) {
+                for (int j = lane; j < half; j += 32) {
                     const float a = to_f32(src[j]), b = to_f32(src[j + half]);
                     const float2 c = cst[j];
                     dst[j] = from_f32<TA>(a * c.x - b * c.y);
                     dst[j + half] = from_f32<TA>(a * c.y + b * c.x);
                 }
                 if (is_k)   // K channels outside the rotated part
-                    for (int c = rot + threadIdx.x; c < rot + rest; c += blockDim.x) dst[c] = src[c];
+                    for (int c = rot + lane; c < rot + rest; c += 32) dst[c] = src[c];
             }
         } else if (write_kv) {
             TA* dst = vdst + (size_t)(slot - nh - nkv) * head_stride;
             if (vec) {
-                for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+                for (int c = lane * 8; c < d; c += 32 * 8) {
                     float a[8];
                     load8(src + c, a);
                     store8(dst + c, a);
                 }
             } else {
-                for (int c = threadIdx.x; c < d; c += blockDim.x) dst[c] = src[c];
+                for (int c = lane; c < d; c += 32) dst[c] = src[c];
             }
         }
     }
@@ -115,7 +118,7 @@ extern "C" int illm_rope_kv_write(void* qkv, const float* cos_sin, const int* to
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(T, (nh + 2 * nkv + RK_SLOTS_PER_BLOCK - 1) / RK_SLOTS_PER_BLOCK);
     if (T > 2147483647 / 2 || grid.y > 65535) return ILLM_ERR_BAD_ARG;
-    int threads = 32;
+    int threads = RK_WARPS * 32;
     if (act_dtype == ILLM_BF16)
         illm_launch(rope_kv_write_kernel<bf16>, dim3(grid), dim3(threads), 0, s, 
             (bf16*)qkv, (const float2*)cos_sin, token_pos, token_seq, block_table, max_pages,

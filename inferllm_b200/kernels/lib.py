@@ -27,6 +27,7 @@ _SIGNATURES = {
     "illm_gemm_bf16_tc": [P, P, P, I, I, I, I, P, I, P, P],
     "illm_gemm_bf16_tc_tune": [I],
     "illm_set_pdl": [I],
+    "illm_attention_prefill_tc": [P, I, I, P, P, LL, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P],
     "illm_gemm_f32_nt": [P, P, P, I, I, I, I, I, I, P],
     "illm_argmax": [P, I, I, I, P, P],
     "illm_sample": [P, I, I, I, P, P, I, F, F, I, F, P, P, P],

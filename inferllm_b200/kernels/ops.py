@@ -227,6 +227,28 @@ def attention_prefill(qkv, k_cache, v_cache, block_table, cu_q, seq_lens, max_q,
     return out
 
 
+def attention_prefill_tc_supported(dtype, n_heads, n_kv_heads, head_dim, page_size) -> bool:
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and n_heads % n_kv_heads == 0
+            and page_size % 64 == 0)
+
+
+def attention_prefill_tc(qkv, k_cache, v_cache, block_table, cu_q, seq_lens, max_q, n_heads, n_kv_heads,
+                         head_dim, page_size, window, scale):
+    """The tcgen05 / TMA version of `attention_prefill` (head size 64 or 128, pages of a
+    multiple of 64 positions)."""
+    _need(qkv, "qkv", torch.bfloat16, 2)
+    _need(k_cache, "k_cache", torch.bfloat16, 4)
+    _need(v_cache, "v_cache", torch.bfloat16, 4)
+    T, B = qkv.shape[0], seq_lens.numel()
+    out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    _check(load().illm_attention_prefill_tc(
+        _ptr(qkv), qkv.shape[1], T, _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table),
+        block_table.shape[1], _ptr(cu_q), _ptr(seq_lens), _ptr(out), B, int(max_q), n_heads, n_kv_heads,
+        head_dim, page_size, int(window or 0), float(scale), _ptr(tc_error_word(qkv.device)), _stream()),
+        "attention_prefill_tc")
+    return out
+
+
 def attention(qkv, kv, ctx, n_heads, n_kv_heads, head_dim, window, scale):
     """Attention of the step's tokens over the cache entry `kv` (a KVView): picks the kernel
     for the dtype, head size and kind of step."""
@@ -236,6 +258,10 @@ def attention(qkv, kv, ctx, n_heads, n_kv_heads, head_dim, window, scale):
         return attention_decode(qkv, kv.k, kv.v, kv.block_table, ctx.token_pos, ctx.token_seq,
                                 n_heads, n_kv_heads, head_dim, kv.page_size, window, scale,
                                 ctx.max_seq_len)
+    if not ctx.is_decode and attention_prefill_tc_supported(qkv.dtype, n_heads, n_kv_heads, head_dim,
+                                                            kv.page_size):
+        return attention_prefill_tc(qkv, kv.k, kv.v, kv.block_table, ctx.cu_q, ctx.seq_lens, ctx.max_q,
+                                    n_heads, n_kv_heads, head_dim, kv.page_size, window, scale)
     if not ctx.is_decode and attention_prefill_supported(qkv.dtype, n_heads, n_kv_heads, head_dim):
         return attention_prefill(qkv, kv.k, kv.v, kv.block_table, ctx.cu_q, ctx.seq_lens, ctx.max_q,
                                  n_heads, n_kv_heads, head_dim, kv.page_size, window, scale)

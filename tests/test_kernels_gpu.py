@@ -296,6 +296,58 @@ def test_attention_prefill(nh, nkv, d, page, window):
     assert maxrel(got, f64(gen)) <= 2 ** -6
 
 
+@pytest.mark.parametrize("nh,nkv,d,page,window", [
+    (2, 2, 128, 64, None), (6, 2, 128, 128, None), (4, 1, 64, 64, None), (3, 3, 64, 128, None),
+    (2, 1, 64, 64, 70), (2, 2, 128, 64, 64), (2, 1, 128, 64, 1), (4, 2, 128, 64, 200)])
+def test_attention_prefill_tc(nh, nkv, d, page, window):
+    """The tcgen05 prompt kernel: prompts shorter than a tile, exactly a tile, several tiles with
+    a ragged end, a chunk that continues a sequence at an odd position, a single token.  The
+    unused places of the cache hold NaN."""
+    lens = [200, 128, 1, 333, 130, 65, 600]
+    starts = [0, 0, 0, 100, 129, 0, 0]
+    pc = Paged(lens, nkv, d, page, torch.bfloat16, seed=d + nh + page)
+    g = torch.Generator().manual_seed(5)
+    q_lens = [n - s for n, s in zip(lens, starts)]
+    T = sum(q_lens)
+    q = torch.randn(T, nh, d, generator=g).bfloat16()
+    qkv = torch.cat([q.reshape(T, nh * d), torch.zeros(T, 2 * nkv * d, dtype=torch.bfloat16)], dim=1)
+    cu = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
+    scale = 1.0 / math.sqrt(d)
+    assert ops.attention_prefill_tc_supported(torch.bfloat16, nh, nkv, d, page)
+    out = ops.attention_prefill_tc(dev(qkv), dev(pc.kc), dev(pc.vc), dev(pc.table), dev(cu),
+                                   dev(torch.tensor(lens, dtype=torch.int32)), max(q_lens), nh, nkv, d, page,
+                                   window, scale)
+    got = f64(out)
+    assert int(ops.tc_error_word(out.device).item()) == 0
+    assert np.isfinite(got).all()
+    for b in range(len(lens)):
+        rows = slice(int(cu[b]), int(cu[b + 1]))
+        ref = plain_attention_rows(f64(q[rows]), f64(pc.k[b]), f64(pc.v[b]), list(range(starts[b], lens[b])),
+                                   nh, nkv, scale, window)
+        assert maxrel(got[rows], ref) <= 2 ** -7, f"sequence {b}"
+
+
+def test_attention_prefill_tc_finds_far_keys_and_respects_the_window_edge():
+    nh = nkv = 1
+    d, page, n = 128, 64, 600
+    pc = Paged([n], nkv, d, page, torch.bfloat16, seed=4)
+    cu, sl = dev(torch.tensor([0, n], dtype=torch.int32)), dev(torch.tensor([n], dtype=torch.int32))
+    for window in (None, 200):
+        for qrow, target in ((599, 2), (599, 399), (599, 400), (300, 101), (300, 100), (77, 77), (128, 127)):
+            key = torch.randn(d, generator=torch.Generator().manual_seed(target))
+            key = (key / key.norm() * 12).bfloat16()
+            kc = pc.kc.clone()
+            kc[int(pc.table[0, target // page]), 0, target % page] = key
+            q = torch.zeros(n, d)
+            q[qrow] = key.float() * 2
+            qkv = torch.cat([q, torch.zeros(n, 2 * d)], dim=1).bfloat16()
+            out = ops.attention_prefill_tc(dev(qkv), dev(kc), dev(pc.vc), dev(pc.table), cu, sl, n, 1, 1, d, page,
+                                           window, 1.0)
+            hit = maxrel(f64(out[qrow]), f64(pc.v[0][target]).reshape(-1)) <= 1e-2
+            inside = target <= qrow and (window is None or target >= qrow - window + 1)
+            assert hit == inside, (window, qrow, target)
+
+
 def test_attention_prefill_finds_far_keys_and_respects_the_window_edge():
     nh = nkv = 1
     d, page, n = 64, 16, 600
