@@ -55,8 +55,45 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const float2* __restr
     const int s1 = min(n_slots, s0 + RK_SLOTS_PER_WARP);
     const float2* cst = cs + (size_t)p * half;
     const int rest = d - rot;
-    // 8 channels per thread with 16-byte accesses where the sizes allow it
+    // 8 channels per thread with 16-byte accesses where the sizes allow it: the warp's lanes are
+    // spread over (head slot, 8-channel chunk) pairs
     const bool vec = ((half & 7) == 0) && ((d & 7) == 0) && ((rot & 7) == 0);
+    if (vec) {
+        const int cpd = d >> 3, hc = half >> 3;      // chunks per head, chunks per rotated half
+        for (int idx = lane; idx < (s1 - s0) * cpd; idx += 32) {
+            const int slot = s0 + idx / cpd, c = idx % cpd;
+            TA* src = row + (size_t)slot * d;
+            if (slot < nh + nkv) {
+                const bool is_k = slot >= nh;
+                if (is_k && !write_kv) continue;
+                TA* dst = is_k ? kdst + (size_t)(slot - nh) * head_stride : src;
+                if (c < hc) {
+                    const int j = c * 8;
+                    float a[8], b[8], ra[8], rb[8];
+                    load8(src + j, a);
+                    load8(src + j + half, b);
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        const float2 cs2 = cst[j + k];
+                        ra[k] = a[k] * cs2.x - b[k] * cs2.y;
+                        rb[k] = a[k] * cs2.y + b[k] * cs2.x;
+                    }
+                    store8(dst + j, ra);
+                    store8(dst + j + half, rb);
+                } else if (c >= 2 * hc && is_k) {       // K channels outside the rotated part
+                    float a[8];
+                    load8(src + c * 8, a);
+                    store8(dst + c * 8, a);
+                }
+            } else if (write_kv) {
+                TA* dst = vdst + (size_t)(slot - nh - nkv) * head_stride;
+                float a[8];
+                load8(src + c * 8, a);
+                store8(dst + c * 8, a);
+            }
+        }
+        return;
+    }
     for (int slot = s0; slot < s1; slot++) {
         TA* src = row + (size_t)slot * d;
         if (slot < nh + nkv) {
