@@ -89,17 +89,3 @@ class DecoderModel:
         part reads host-side fields of the step context (a mixer says so with `graph_safe`)."""
         return all(getattr(b.mixer, "graph_safe", False) and getattr(b.ffn, "graph_safe", True)
                    for b in self.blocks)
-
-    # ---- figures for the roofline
-
-    def weight_bytes_per_step(self) -> int:
-        """Bytes of the weights that one decode step reads (the embedding table is gathered,
-        not streamed, unless it is also the head)."""
-        total = 0
-        for _, part in self._owners():
-            if part is self.embedding and not self.head.tied:
-                continue
-            for attr in vars(part).values():
-                if hasattr(attr, "numel") and hasattr(attr, "element_size") and getattr(attr, "is_cuda", False):
-                    total += attr.numel() * attr.element_size()
-        return total

@@ -97,18 +97,21 @@ def test_temperature_sampling_is_reproducible_and_batch_independent(model_folder
 
 
 def test_repeat_penalty_changes_greedy_choice(model_folders, plain_models):
+    """Greedy with a repetition penalty picks what the reference's sampler ranks first: the
+    penalised maximum.  The prompt ends with the model's own favourite, which the penalty demotes."""
     name = "A"
     cfg, w = plain_models[name]
     p = random_prompt(name, 20, 5)
-    logits = plain.forward(cfg, w, p)[-1]
-    top = int(np.argmax(logits))
+    top = int(np.argmax(plain.forward(cfg, w, p)[-1]))
+    prompt = p + [top]
+    logits = plain.forward(cfg, w, prompt)[-1]
+    ids, _ = plain.sample_distribution(logits, prompt, 1.5, 1, 1.0, 1.0)
     m = load(model_folders[name], "float32", nr_ctx=128)
-    m.init(top_k=0, top_p=1.0, temp=0.0, repeat_penalty=1e6, repeat_last_n=64, seed=0, end_token=-1)
-    # the prompt's own tokens are penalised; put the favourite into the prompt and it loses
-    tok = m.generate([p + [top]], max_new_tokens=1, stop_ids=[]).tokens[0][0]
-    lg2 = plain.forward(cfg, w, p + [top])[-1]
-    ids, _ = plain.sample_distribution(lg2, p + [top], 1e6, 1, 1.0, 1.0)
-    assert tok == int(ids[0]) and tok not in set(p + [top]) or lg2[tok] < 0
+    m.init(top_k=0, top_p=1.0, temp=0.0, repeat_penalty=1.5, repeat_last_n=64, seed=0, end_token=-1)
+    tok = m.generate([prompt], max_new_tokens=1, stop_ids=[]).tokens[0][0]
+    assert tok == int(ids[0])
+    m.init(top_k=0, top_p=1.0, temp=0.0, repeat_penalty=1.0, repeat_last_n=64, seed=0, end_token=-1)
+    assert m.generate([prompt], max_new_tokens=1, stop_ids=[]).tokens[0][0] == int(np.argmax(logits))
 
 
 def test_command_line(model_folders, plain_models, tmp_path):
