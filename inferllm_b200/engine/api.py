@@ -13,7 +13,7 @@ from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
 from ..sampling import Sampler, SamplingParams
-from .generate import GenerationResult, generate
+from .generate import GenerationResult, generate, generate_pipelined
 from .step import Engine, EngineError, EngineOptions, StepItem
 
 
@@ -147,6 +147,9 @@ class Model:
         if stop_ids is None:
             stop_ids = [] if self.end_token is None else [self.end_token]
         sampler = Sampler(self.sampling)
-        res = generate(self.engine, prompts, sampler.choose, max_new_tokens, stop_ids, on_token)
+        # without a repetition penalty the sampler needs no token history on the host, and the
+        # loop can keep the host one step behind the device
+        loop = generate_pipelined if self.sampling.repeat_penalty == 1.0 else generate
+        res = loop(self.engine, prompts, sampler.choose, max_new_tokens, stop_ids, on_token)
         self.engine.check_device_errors()
         return res

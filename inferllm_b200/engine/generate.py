@@ -33,6 +33,7 @@ class GenerationResult:
     decode_tokens: int = 0
     decode_s: float = 0.0
     decode_steps: int = 0
+    step_s: List[float] = field(default_factory=list)    # wall time of every decode step, in order
 
     def summary(self) -> str:
         pf = self.prefill_tokens / self.prefill_s if self.prefill_s > 0 else 0.0
@@ -117,7 +118,8 @@ def generate(backend, prompts: Sequence[Sequence[int]], choose: Callable, max_ne
                         continue
                     backend.end_sequence(slots.pop(r))
                 if not first:
-                    res.decode_s += clock() - t0
+                    res.step_s.append(clock() - t0)
+                    res.decode_s += res.step_s[-1]
                     res.decode_tokens += len(live)
                     res.decode_steps += 1
                 first = False
@@ -128,6 +130,83 @@ def generate(backend, prompts: Sequence[Sequence[int]], choose: Callable, max_ne
                 logits = backend.step([StepItem(slots[r], [hist[r][-1]], [0]) for r in live])
                 toks = _as_list(choose(logits, live, [len(res.tokens[r]) for r in live],
                                        [hist[r] for r in live]))
+        finally:
+            for s in slots.values():
+                backend.end_sequence(s)
+    return res
+
+
+def generate_pipelined(backend, prompts: Sequence[Sequence[int]], choose: Callable, max_new_tokens: int,
+                       stop_ids: Sequence[int] = (), on_token: Optional[Callable] = None,
+                       clock: Callable = time.perf_counter) -> GenerationResult:
+    """The same loop with the host one step behind the device.  The sampled tokens stay on the
+    device and feed the next step directly (`backend.step(..., device_ids=...)`); the host reads
+    them only afterwards, while that next step already runs, so its own work (bookkeeping, packing
+    and launching a step) no longer adds to the time per token.  A sequence that turns out to have
+    sampled a stop token has then already been run one step too far: that step's result for it is
+    dropped and its slot is freed, which changes nothing for the others (a sequence's logits do
+    not depend on the rest of its batch).  `choose` must return a device tensor and must not need
+    the histories (no repetition penalty): `generate` is the loop for everything else."""
+    limits: Limits = backend.limits()
+    stop = set(int(s) for s in stop_ids)
+    n = len(prompts)
+    res = GenerationResult([[] for _ in range(n)], [""] * n,
+                           plan_batches([len(p) for p in prompts], max_new_tokens, limits))
+    if max_new_tokens <= 0:
+        res.finish = ["length"] * n
+        return res
+    for batch in res.batches:
+        slots = {r: backend.new_sequence() for r in batch}
+        n_fed = {r: len(prompts[r]) for r in batch}          # tokens of r that the cache holds
+        try:
+            t0 = clock()
+            logits = backend.step([StepItem(slots[r], list(prompts[r]), [len(prompts[r]) - 1]) for r in batch])
+            pending, pending_toks = list(batch), choose(logits, batch, [0] * len(batch), None)
+            first = True
+            while pending:
+                # who goes on if the token just sampled is no stop token: decided by counts alone
+                n_tok = {r: len(res.tokens[r]) + 1 for r in pending}
+                cont = [r for r in pending if n_tok[r] < max_new_tokens and n_fed[r] + 1 <= limits.max_seq_len]
+                nxt_toks = None
+                if cont:
+                    idx = [pending.index(r) for r in cont]
+                    feed = pending_toks if len(cont) == len(pending) else pending_toks[idx]
+                    logits = backend.step([StepItem(slots[r], [0], [0]) for r in cont], device_ids=feed)
+                    for r in cont:
+                        n_fed[r] += 1
+                    nxt_toks = choose(logits, cont, [n_tok[r] for r in cont], None)
+                toks = _as_list(pending_toks)                 # waits for the sampling before the step above
+                now = clock()
+                if first:
+                    res.prefill_s += now - t0
+                    res.prefill_tokens += sum(len(prompts[r]) for r in batch)
+                    first = False
+                else:
+                    res.step_s.append(now - t0)
+                    res.decode_s += now - t0
+                    res.decode_tokens += len(pending)
+                    res.decode_steps += 1
+                t0 = now
+                stopped = set()
+                for r, tok in zip(pending, toks):
+                    res.tokens[r].append(tok)
+                    if on_token:
+                        on_token(r, tok)
+                    if tok in stop:
+                        res.finish[r] = "stop"
+                        stopped.add(r)
+                    elif len(res.tokens[r]) >= max_new_tokens:
+                        res.finish[r] = "length"
+                    elif r not in cont:
+                        res.finish[r] = "context"
+                    else:
+                        continue
+                    backend.end_sequence(slots.pop(r))
+                if stopped & set(cont):
+                    keep = [i for i, r in enumerate(cont) if r not in stopped]
+                    nxt_toks = nxt_toks[keep] if keep else None
+                    cont = [cont[i] for i in keep]
+                pending, pending_toks = cont, nxt_toks
         finally:
             for s in slots.values():
                 backend.end_sequence(s)

@@ -72,17 +72,20 @@ class StepContext:
         static input of a captured graph); None uploads into a fresh buffer."""
         cache = engine.cache
         B = len(plan.slots)
-        q = np.asarray(plan.q_lens, dtype=np.int64)
-        past = np.asarray(plan.past, dtype=np.int64)
+        q = np.asarray(plan.q_lens, dtype=np.int32)
+        past = np.asarray(plan.past, dtype=np.int32)
         T = int(q.sum())
-        cu = np.zeros(B + 1, dtype=np.int64)
-        np.cumsum(q, out=cu[1:])
-        token_seq = np.repeat(np.arange(B), q)
-        token_pos = np.arange(T) - np.repeat(cu[:-1], q) + np.repeat(past, q)
-        parts = [np.asarray(ids_host, dtype=np.int32), token_pos.astype(np.int32),
-                 token_seq.astype(np.int32), np.asarray(want_rows_host, dtype=np.int32),
-                 np.asarray(plan.slots, dtype=np.int32), (past + q).astype(np.int32),
-                 cu.astype(np.int32)] + [t.reshape(-1) for t in plan.tables]
+        if T == B:                       # one token per sequence: no arithmetic needed
+            cu = np.arange(B + 1, dtype=np.int32)
+            token_seq, token_pos = cu[:-1], past
+        else:
+            cu = np.zeros(B + 1, dtype=np.int32)
+            np.cumsum(q, out=cu[1:])
+            token_seq = np.repeat(np.arange(B, dtype=np.int32), q)
+            token_pos = np.arange(T, dtype=np.int32) - np.repeat(cu[:-1], q) + np.repeat(past, q)
+        parts = [np.asarray(ids_host, dtype=np.int32), token_pos, token_seq,
+                 np.asarray(want_rows_host, dtype=np.int32), np.asarray(plan.slots, dtype=np.int32),
+                 past + q, cu] + [t.reshape(-1) for t in plan.tables]
         offs, total = [], 0
         for p in parts:
             offs.append(total)
@@ -134,8 +137,8 @@ class Engine:
         self.cache = SequenceCache(self.model.cache_requests(), num_slots, num_pages, ps, max_seq,
                                    self.rt)
         self.err = torch.zeros(1, dtype=torch.int32, device=dev)
-        self._stage = None
-        self._staging_busy = None
+        self._stages = [(None, None, None)] * 4    # (pinned tensor, its numpy view, copy-done event)
+        self._stage_next = 0
         self._graphs = {}
         self._graph_pool = None
         self.loaded = False
@@ -185,24 +188,34 @@ class Engine:
     # ---- the step
 
     def _upload(self, parts, offs, total: int, into=None) -> torch.Tensor:
-        """One pinned staging buffer, one asynchronous copy for all of a step's index arrays."""
-        if self._staging_busy is not None:
-            self._staging_busy.synchronize()  # the previous step's copy has left the buffer
-        if self._stage is None or self._stage.numel() < total:
-            self._stage = torch.empty(max(total, 4096), dtype=torch.int32, pin_memory=True)
-        host = self._stage
+        """One asynchronous copy for all of a step's index arrays, from a small ring of pinned
+        staging buffers: the host may prepare the next steps while the GPU still runs this one,
+        and waits only when it comes back to a buffer whose copy has not left yet."""
+        slot = self._stage_next
+        self._stage_next = (slot + 1) % len(self._stages)
+        stage, stage_np, busy = self._stages[slot]
+        if busy is not None:
+            busy.synchronize()
+        if stage is None or stage.numel() < total:
+            stage = torch.empty(max(total, 4096), dtype=torch.int32, pin_memory=True)
+            stage_np = stage.numpy()      # the same pinned memory, for cheap fills
         for o, p in zip(offs, parts):
-            host[o:o + p.size] = torch.from_numpy(p)
+            stage_np[o:o + p.size] = p
         buf = into if into is not None else torch.empty(total, dtype=torch.int32, device=self.rt.device)
-        buf.copy_(host[:total], non_blocking=True)
+        buf.copy_(stage[:total], non_blocking=True)
         self.last_upload_bytes = 4 * total
-        self._staging_busy = torch.cuda.Event()
-        self._staging_busy.record()
+        busy = torch.cuda.Event()
+        busy.record()
+        self._stages[slot] = (stage, stage_np, busy)
         return buf
 
-    def step(self, items: Sequence[StepItem]) -> torch.Tensor:
+    def step(self, items: Sequence[StepItem], device_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run one step; returns float32 logits [number of wanted places, vocab] on the device,
-        in the order of the items and of each item's `want`."""
+        in the order of the items and of each item's `want`.
+
+        `device_ids` (int32 tensor on the device, one id per item) gives the tokens of a
+        one-token-per-sequence step without a round trip through the host, e.g. straight from the
+        sampling kernel; the items' `tokens` are then placeholders of length one."""
         if not self.loaded:
             raise EngineError("the model has no weights yet")
         if not items:
@@ -222,15 +235,21 @@ class Engine:
                 want_rows.append(off + int(w))
             ids.extend(int(t) for t in it.tokens)
             off += n
+        if device_ids is not None and (len(ids) != len(items) or device_ids.numel() != len(items)
+                                       or device_ids.dtype != torch.int32):
+            raise EngineError("device_ids needs one int32 id per item and items of one token each")
         plan = self.cache.plan_step([it.slot for it in items], [len(it.tokens) for it in items])
         if self.options.cuda_graphs and len(ids) == len(items) and self.model.graph_safe():
-            logits = self._decode_step_graphed(plan, ids, want_rows)
+            logits = self._decode_step_graphed(plan, ids, want_rows, device_ids)
         else:
-            logits = self.model.forward(StepContext(self, plan, ids, want_rows))
+            ctx = StepContext(self, plan, ids, want_rows)
+            if device_ids is not None:
+                ctx.ids.copy_(device_ids)
+            logits = self.model.forward(ctx)
         self.cache.commit_step(plan)
         return logits
 
-    def _decode_step_graphed(self, plan, ids, want_rows) -> torch.Tensor:
+    def _decode_step_graphed(self, plan, ids, want_rows, device_ids=None) -> torch.Tensor:
         """One token per sequence: the launches of such a step are the same every time (all that
         changes lies in device memory), so the step is captured in a CUDA graph the second time
         a batch size is seen and replayed from then on.  The logits of a replayed step are
@@ -239,11 +258,16 @@ class Engine:
         entry = self._graphs.get(key)
         if entry is None:
             self._graphs[key] = "seen"
-            return self.model.forward(StepContext(self, plan, ids, want_rows))
+            ctx = StepContext(self, plan, ids, want_rows)
+            if device_ids is not None:
+                ctx.ids.copy_(device_ids)
+            return self.model.forward(ctx)
         if entry == "seen":
             if len(self._graphs) > 64:
                 self._graphs = {k: v for k, v in self._graphs.items() if v == "seen"}
             ctx = StepContext(self, plan, ids, want_rows)
+            if device_ids is not None:
+                ctx.ids.copy_(device_ids)
             torch.cuda.current_stream().synchronize()
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
@@ -257,6 +281,8 @@ class Engine:
             return out.clone()
         graph, ctx, out, launches = entry
         StepContext(self, plan, ids, want_rows, into=ctx.buffer)
+        if device_ids is not None:
+            ctx.ids.copy_(device_ids)
         graph.replay()
         ops.count_launches(launches)
         return out.clone()

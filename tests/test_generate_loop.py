@@ -1,7 +1,9 @@
 """Decisions of the generation loop, with stand-ins for the engine and the sampler (no GPU)."""
 import pytest
 
-from inferllm_b200.engine import Limits, RequestTooLong, generate, plan_batches
+import torch
+
+from inferllm_b200.engine import Limits, RequestTooLong, generate, generate_pipelined, plan_batches
 
 
 class FakeBackend:
@@ -13,6 +15,7 @@ class FakeBackend:
         self.free = list(range(max_batch))[::-1]
         self.len = {}
         self.log = []
+        self.fed = []
         self.peak_pages = 0
 
     def limits(self):
@@ -28,8 +31,11 @@ class FakeBackend:
         del self.len[slot]
         self.free.append(slot)
 
-    def step(self, items):
+    def step(self, items, device_ids=None):
         assert len({it.slot for it in items}) == len(items)
+        if device_ids is not None:
+            assert len(device_ids) == len(items) and all(len(it.tokens) == 1 for it in items)
+            self.fed.append([int(t) for t in device_ids])
         out = []
         for it in items:
             assert it.slot in self.len and len(it.tokens) >= 1
@@ -135,3 +141,29 @@ def test_zero_new_tokens():
     be = FakeBackend()
     res = generate(be, [[1]], scripted({0: []}), max_new_tokens=0)
     assert res.tokens == [[]] and be.log == []
+
+
+def tensor_script(script):
+    def choose(logits, requests, steps, histories):
+        return torch.tensor([script[r][s] for r, s in zip(requests, steps)], dtype=torch.int32)
+    return choose
+
+
+@pytest.mark.parametrize("max_new,stop,max_seq", [(5, [9], 16), (3, [], 16), (10, [9], 6), (1, [9], 16), (4, [7, 4], 16)])
+def test_pipelined_loop_makes_the_same_decisions(max_new, stop, max_seq):
+    """The loop that keeps the host one step behind the device returns what the plain loop
+    returns, feeds the tokens it sampled, and gives every slot back, although sequences that hit
+    a stop token have been run one step too far."""
+    prompts = [[1, 2, 3], [1], [5, 5], [2, 2, 2, 2], [8]]
+    script = {0: [7, 9, 8, 8, 8, 1, 1, 1, 1, 1], 1: [4, 4, 4, 9, 8, 1, 1, 1, 1, 1], 2: [9] * 10, 3: [3] * 10,
+              4: [6, 6, 6, 6, 6, 6, 6, 9, 9, 9]}
+    a = FakeBackend(max_batch=3, num_pages=12, page_size=4, max_seq_len=max_seq)
+    b = FakeBackend(max_batch=3, num_pages=12, page_size=4, max_seq_len=max_seq)
+    want = generate(a, prompts, scripted(script), max_new, stop)
+    got = generate_pipelined(b, prompts, tensor_script(script), max_new, stop)
+    assert got.tokens == want.tokens and got.finish == want.finish and got.batches == want.batches
+    assert b.len == {} and sorted(b.free) == [0, 1, 2]
+    # every token fed back is one that was sampled for that step
+    flat = [t for step in b.fed for t in step]
+    assert all(t in {x for v in script.values() for x in v} for t in flat)
+    assert got.decode_tokens + len(prompts) == sum(len(t) for t in got.tokens)

@@ -44,8 +44,8 @@ class PartHarness:
                           page_size)
         self.cache = SequenceCache(requests, num_slots, num_pages, page_size, max_seq_len, self.rt)
         self.err = torch.zeros(1, dtype=torch.int32, device="cuda")
-        self._stage = None
-        self._staging_busy = None
+        self._stages = [(None, None, None)] * 4
+        self._stage_next = 0
 
     def _upload(self, parts, offs, total, into=None):
         from inferllm_b200.engine import Engine
