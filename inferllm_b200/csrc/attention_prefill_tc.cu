@@ -1,21 +1,21 @@
 // Causal attention of whole prompts over the paged cache on the 5th-generation tensor cores.
 //
-// One block owns 128 consecutive query tokens of one (sequence, head); a thread of its four
-// softmax warps owns one query row, which is also one lane of tensor memory.  Keys and values
-// come in blocks of 128 straight from the cache pages by TMA (two pages of 64 positions, 128-byte
-// swizzle, double buffered).  Per block of keys:
-//   S = Q K^T      tcgen05.mma, M = 128 rows, N = 128 keys, K = head size, accumulator in tensor
-//                  memory columns [0, 128)
+// One block owns two tiles of 128 consecutive query tokens of one (sequence, head); each tile has
+// four softmax warps of its own, a thread of which owns one query row, which is also one lane of
+// tensor memory.  Keys and values come in blocks of 64 straight from the cache pages by TMA
+// (128-byte swizzle, double buffered) and serve both tiles.  Per tile and block of keys:
+//   S = Q K^T      tcgen05.mma, M = 128 rows, N = 64 keys, K = head size, accumulator in the
+//                  tile's tensor memory columns [0, 64)
 //   softmax        each thread reads its row of S with tcgen05.ld, scales, masks (causal, window),
 //                  keeps the running maximum and sum in float32, and writes P = exp2(S - max) as
 //                  bfloat16 into shared memory in the swizzled layout the tensor core reads
 //   O_blk = P V    tcgen05.mma with V as an MN-major operand (the cache keeps [position, channel]),
-//                  into columns [128, 128 + head size); the thread adds it to its row of O, which it
+//                  into columns [64, 64 + head size); the thread adds it to its row of O, which it
 //                  keeps in registers, after scaling O by exp2(old max - new max)
 // so the score matrix never exists in memory and nothing of the running state crosses threads.
-// One more thread issues the MMAs and another the TMA copies; the MMA of the next block's scores
-// is issued together with P V of the current one, so the tensor core works while the softmax
-// warps accumulate.  Formulas as in the reference (src/kern/naive/naive.cpp:606-632, :531-553,
+// One more thread issues the MMAs and another the TMA copies; the MMAs of one tile run while the
+// softmax warps of the other tile work, and the scores of a tile's next block are issued right
+// behind its P V.  Formulas as in the reference (src/kern/naive/naive.cpp:606-632, :531-553,
 // :209-240, :664-691), which materialises S in float32 and runs four launches over it
 // (src/kern/gpu/kernel_gpu.cu:576-609, :504-536, :78-125).
 // Takes head sizes 64 and 128 and page sizes that are multiples of 64; any number of heads and
@@ -26,9 +26,10 @@
 
 #include "common.cuh"
 
-#define FT_BM 128
-#define FT_BN 128
-#define FT_THREADS 192
+#define FT_BM 128            // rows of a query tile = lanes of tensor memory
+#define FT_MAX_TILES 2       // query tiles per block: one's softmax overlaps the other's MMAs
+#define FT_BN 64             // keys per ring block (one page piece)
+#define FT_THREADS(tiles) (32 * (4 * (tiles) + 2))
 #define FT_WAIT_LIMIT (1 << 22)
 #define FT_ERR_TIMEOUT 5
 
@@ -106,31 +107,36 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, float* v) {
 
 }  // namespace
 
-template <int D>
-__global__ void __launch_bounds__(FT_THREADS)
+template <int D, int FT_TILES>
+__global__ void __launch_bounds__(FT_THREADS(FT_TILES), FT_TILES == 1 ? 2 : 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                             int max_pages, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
                             bf16* __restrict__ out, int nh, int nkv, int page_size, int window,
                             float scale_log2e, int* __restrict__ err) {
+    constexpr int FT_MMA_WARP = 4 * FT_TILES, FT_TMA_WARP = 4 * FT_TILES + 1;
     constexpr int NA = D / 64;                            // 64-channel atoms of the head
-    constexpr unsigned Q_BYTES = FT_BM * D * 2;           // [NA][128 rows][128 B]
-    constexpr unsigned KV_BYTES = FT_BN * D * 2;          // K: [NA][128 keys][128 B]; V: the same shape
-    constexpr unsigned P_BYTES = FT_BM * FT_BN * 2;       // [2 atoms of 64 keys][128 rows][128 B]
-    constexpr unsigned HALF_BYTES = 64 * 128;             // 64 positions x 64 channels
-    constexpr unsigned ATOM_BYTES = 128 * 128;            // 128 rows x 128 B
-    constexpr unsigned TMEM_COLS = 256;
-    constexpr unsigned O_COL = 128;
+    constexpr unsigned Q_TILE = FT_BM * D * 2;            // one query tile: [NA][128 rows][128 B]
+    constexpr unsigned KV_BYTES = FT_BN * D * 2;          // K: [NA][64 keys][128 B]; V: the same shape
+    constexpr unsigned P_TILE = FT_BM * FT_BN * 2;        // [128 rows][128 B] = 64 keys
+    constexpr unsigned Q_ATOM = 128 * 128, KV_ATOM = FT_BN * 128;
+    constexpr unsigned TMEM_COLS = 256 * FT_TILES, TILE_COLS = 256, O_COL = FT_BN;   // one-tile blocks share an SM
     constexpr unsigned IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(FT_BN >> 3) << 17) | ((unsigned)(FT_BM >> 4) << 24);
     constexpr unsigned IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(D >> 3) << 17) | ((unsigned)(FT_BM >> 4) << 24);
 
-    extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) unsigned long long bars[9];
-    __shared__ unsigned tmem_holder;
-    const unsigned base = (s_u32(smem_raw) + 1023u) & ~1023u;
-    const unsigned q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + 2 * KV_BYTES, p_s = v_s + 2 * KV_BYTES;
-    const unsigned q_full = s_u32(&bars[0]), kv_full0 = s_u32(&bars[1]), kv_empty0 = s_u32(&bars[3]);
-    const unsigned s_full = s_u32(&bars[5]), p_full = s_u32(&bars[6]), o_full = s_u32(&bars[7]);
+    // No static shared memory: the dynamic window then starts on a 1024-byte boundary (the
+    // swizzle's period) and two one-tile blocks fit an SM.  Barriers sit behind the tiles.
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const unsigned base = s_u32(smem_raw);
+    const unsigned q_s = base, k_s = q_s + FT_TILES * Q_TILE, v_s = k_s + 2 * KV_BYTES, p_s = v_s + 2 * KV_BYTES;
+    const unsigned bars0 = p_s + FT_TILES * P_TILE;
+    unsigned* tmem_holder_p = reinterpret_cast<unsigned*>(smem_raw + (bars0 - base) + 11 * 8);
+    const unsigned q_full = bars0, kv_full0 = bars0 + 8, kv_empty0 = bars0 + 24;
+    const unsigned s_full0 = bars0 + 40, p_full0 = bars0 + 56, o_full0 = bars0 + 72;
+    if ((base & 1023u) != 0) {          // cannot happen without static shared memory; never run misaligned
+        if (threadIdx.x == 0) atomicExch(err, FT_ERR_TIMEOUT + 1);
+        return;
+    }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -138,110 +144,139 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int i = 0; i < 2; i++) {
             bar_init(kv_full0 + 8 * i, 1);
             bar_init(kv_empty0 + 8 * i, 1);
+            bar_init(s_full0 + 8 * i, 1);
+            bar_init(p_full0 + 8 * i, FT_BM);
+            bar_init(o_full0 + 8 * i, 1);
         }
-        bar_init(s_full, 1);
-        bar_init(p_full, FT_BM);
-        bar_init(o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 4) {
+    if (warp == FT_MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(s_u32(&tmem_holder)), "r"(TMEM_COLS) : "memory");
+                     ::"r"(s_u32(tmem_holder_p)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     fence_before();
     __syncthreads();
     fence_after();
-    const unsigned tmem = tmem_holder;
+    const unsigned tmem = *tmem_holder_p;
     pdl_grid_sync();
 
-    // ---- which rows and keys (the last tiles of a prompt see the most keys and start first)
-    const int b = blockIdx.z, h = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
+    // ---- which rows and keys.  The block owns FT_TILES query tiles of 128 rows; the last blocks of
+    // a prompt see the most keys and start first.
+    const int b = blockIdx.z, h = blockIdx.y, cta_tile = gridDim.x - 1 - blockIdx.x;
     const int q0 = cu_q[b], qlen = cu_q[b + 1] - q0;
-    const int row0 = tile * FT_BM;
-    const bool has_rows = row0 < qlen;
+    const int cta_row0 = cta_tile * FT_TILES * FT_BM;
     const int total = seq_lens[b], past = total - qlen;
     const int hk = h / (nh / nkv);
-    const int rows_here = has_rows ? ((qlen - row0 < FT_BM) ? qlen - row0 : FT_BM) : 0;
-    const int first_pos = past + row0, last_pos = first_pos + rows_here - 1;
-    const int lo_key = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
-    const int jb0 = lo_key / FT_BN, jb1 = has_rows ? last_pos / FT_BN : -1;
-    const int n_blocks = jb1 - jb0 + 1;
+    const int cta_rows = (qlen - cta_row0 < FT_TILES * FT_BM) ? qlen - cta_row0 : FT_TILES * FT_BM;   // <= 0: nothing
+    const bool cta_has_rows = cta_rows > 0;
+    const int cta_first_pos = past + cta_row0, cta_last_pos = cta_first_pos + cta_rows - 1;
+    const int lo_key = (window > 0 && cta_first_pos - window + 1 > 0) ? cta_first_pos - window + 1 : 0;
+    const int jb0 = lo_key / FT_BN;                               // first key block of the block's ring
+    const int n_blocks = cta_has_rows ? cta_last_pos / FT_BN - jb0 + 1 : 0;
     const int* bt = block_table + (size_t)b * max_pages;
+    // per tile: rows, and the range [lo_t, hi_t) of ring blocks it needs (ring block i = key block jb0 + i)
+    int rows_t[FT_TILES], lo_t[FT_TILES], hi_t[FT_TILES];
+#pragma unroll
+    for (int t = 0; t < FT_TILES; t++) {
+        const int r0 = cta_row0 + t * FT_BM;
+        rows_t[t] = (qlen - r0 < FT_BM) ? qlen - r0 : FT_BM;
+        if (rows_t[t] < 0) rows_t[t] = 0;
+        const int fp = past + r0, lp = fp + rows_t[t] - 1;
+        const int lk = (window > 0 && fp - window + 1 > 0) ? fp - window + 1 : 0;
+        lo_t[t] = rows_t[t] > 0 ? lk / FT_BN - jb0 : 0;
+        hi_t[t] = rows_t[t] > 0 ? lp / FT_BN - jb0 + 1 : 0;
+    }
 
-    if (warp == 5) {
+    if (warp == FT_TMA_WARP) {
         // ---- TMA producer
-        if (lane == 0 && has_rows) {
-            bar_expect_tx(q_full, Q_BYTES);
-            for (int a = 0; a < NA; a++) tma_2d(q_s + a * ATOM_BYTES, &map_q, h * D + 64 * a, q0 + row0, q_full);
+        if (lane == 0 && cta_has_rows) {
+            bar_expect_tx(q_full, FT_TILES * Q_TILE);
+            for (int t = 0; t < FT_TILES; t++)
+                for (int a = 0; a < NA; a++)
+                    tma_2d(q_s + t * Q_TILE + a * Q_ATOM, &map_q, h * D + 64 * a, q0 + cta_row0 + t * FT_BM, q_full);
             bool alive = true;
             for (int i = 0; i < n_blocks && alive; i++) {
                 const int buf = i & 1;
                 if (i >= 2) alive = bar_wait(kv_empty0 + 8 * buf, ((i >> 1) - 1) & 1, err);
                 if (!alive) break;
                 const int key0 = (jb0 + i) * FT_BN;
-                const int halves = (key0 + 64 <= last_pos) ? 2 : 1;     // 64-position pieces that hold keys
-                bar_expect_tx(kv_full0 + 8 * buf, (unsigned)halves * NA * HALF_BYTES * 2);
-                for (int hf = 0; hf < halves; hf++) {
-                    const int key = key0 + 64 * hf;
-                    const int page = bt[key / page_size];
-                    const int row = (page * nkv + hk) * page_size + (key % page_size);
-                    for (int a = 0; a < NA; a++) {
-                        const unsigned off = buf * KV_BYTES + a * ATOM_BYTES + hf * HALF_BYTES;
-                        tma_2d(k_s + off, &map_k, 64 * a, row, kv_full0 + 8 * buf);
-                        tma_2d(v_s + off, &map_v, 64 * a, row, kv_full0 + 8 * buf);
-                    }
+                const int page = bt[key0 / page_size];
+                const int row = (page * nkv + hk) * page_size + (key0 % page_size);
+                bar_expect_tx(kv_full0 + 8 * buf, 2 * KV_BYTES);
+                for (int a = 0; a < NA; a++) {
+                    tma_2d(k_s + buf * KV_BYTES + a * KV_ATOM, &map_k, 64 * a, row, kv_full0 + 8 * buf);
+                    tma_2d(v_s + buf * KV_BYTES + a * KV_ATOM, &map_v, 64 * a, row, kv_full0 + 8 * buf);
                 }
             }
         }
-    } else if (warp == 4) {
-        // ---- MMA issuer
-        if (lane == 0 && has_rows) {
+    } else if (warp == FT_MMA_WARP) {
+        // ---- MMA issuer: for every ring block, P V of each tile as soon as its P is there, and the
+        // scores of the next block for that tile right behind it
+        if (lane == 0 && cta_has_rows) {
             bool alive = bar_wait(q_full, 0, err);
-            auto issue_s = [&](int i) {
+            int n_s[FT_TILES], n_p[FT_TILES];     // how many S / P V products each tile has been issued
+#pragma unroll
+            for (int t = 0; t < FT_TILES; t++) n_s[t] = n_p[t] = 0;
+            auto issue_s = [&](int t, int i) {
                 const int buf = i & 1;
                 if (!bar_wait(kv_full0 + 8 * buf, (i >> 1) & 1, err)) return false;
                 fence_after();
 #pragma unroll
                 for (int kk = 0; kk < D / 16; kk++) {
-                    const unsigned o = (kk >> 2) * ATOM_BYTES + (kk & 3) * 32;
-                    mma_bf16_ss(tmem, desc_kmajor(q_s + o), desc_kmajor(k_s + buf * KV_BYTES + o), IDESC_S, kk > 0);
+                    const unsigned qo = t * Q_TILE + (kk >> 2) * Q_ATOM + (kk & 3) * 32;
+                    const unsigned ko = buf * KV_BYTES + (kk >> 2) * KV_ATOM + (kk & 3) * 32;
+                    mma_bf16_ss(tmem + t * TILE_COLS, desc_kmajor(q_s + qo), desc_kmajor(k_s + ko), IDESC_S, kk > 0);
                 }
-                mma_commit(s_full);
+                mma_commit(s_full0 + 8 * t);
+                n_s[t]++;
                 return true;
             };
-            if (alive) alive = issue_s(0);
+#pragma unroll
+            for (int t = 0; t < FT_TILES; t++)
+                if (alive && lo_t[t] == 0 && hi_t[t] > 0) alive = issue_s(t, 0);
             for (int i = 0; i < n_blocks && alive; i++) {
                 const int buf = i & 1;
-                alive = bar_wait(p_full, i & 1, err);
-                if (!alive) break;
-                fence_after();
 #pragma unroll
-                for (int ks = 0; ks < FT_BN / 16; ks++) {
-                    const unsigned po = (ks >> 2) * ATOM_BYTES + (ks & 3) * 32;   // P: K-major, K = keys
-                    const unsigned vo = buf * KV_BYTES + ks * 16 * 128;           // V: 16 positions further
-                    mma_bf16_ss(tmem + O_COL, desc_kmajor(p_s + po), desc_mnmajor(v_s + vo, ATOM_BYTES), IDESC_O, ks > 0);
+                for (int t = 0; t < FT_TILES; t++) {
+                    if (!alive) break;
+                    if (i >= lo_t[t] && i < hi_t[t]) {
+                        alive = bar_wait(p_full0 + 8 * t, n_p[t] & 1, err);
+                        if (!alive) break;
+                        fence_after();
+#pragma unroll
+                        for (int ks = 0; ks < FT_BN / 16; ks++)
+                            mma_bf16_ss(tmem + t * TILE_COLS + O_COL, desc_kmajor(p_s + t * P_TILE + ks * 32),
+                                        desc_mnmajor(v_s + buf * KV_BYTES + ks * 16 * 128, KV_ATOM), IDESC_O, ks > 0);
+                        mma_commit(o_full0 + 8 * t);
+                        n_p[t]++;
+                    }
+                    // after the last tile's products: everything that reads this ring block has been
+                    // issued, so its completion frees the block for the loader
+                    if (t == FT_TILES - 1) mma_commit(kv_empty0 + 8 * buf);
+                    if (i + 1 >= lo_t[t] && i + 1 < hi_t[t]) alive = issue_s(t, i + 1);
                 }
-                mma_commit(o_full);
-                mma_commit(kv_empty0 + 8 * buf);
-                if (i + 1 < n_blocks) alive = issue_s(i + 1);
             }
         }
-    } else if (has_rows) {
+    } else if (warp < 4 * FT_TILES) {
         // ---- softmax and accumulation: thread = query row = lane of tensor memory
-        const int r = threadIdx.x;                       // 0..127
-        const unsigned lane_addr = (unsigned)(warp * 32) << 16;
-        const int pos = (r < rows_here) ? first_pos + r : last_pos;
+        const int t = warp >> 2;                          // which tile this warp group works on
+        const int r = threadIdx.x & 127;                  // row inside the tile
+        const unsigned lane_addr = ((unsigned)((warp & 3) * 32) << 16) + t * TILE_COLS;
+        const int first_pos = cta_first_pos + t * FT_BM;
+        const int last_pos = first_pos + rows_t[t] - 1;
+        const int pos = (r < rows_t[t]) ? first_pos + r : last_pos;
         float m_run = -INFINITY, l_run = 0.f;
         float o_reg[D];
 #pragma unroll
         for (int c = 0; c < D; c++) o_reg[c] = 0.f;
         bool alive = true;
-        for (int i = 0; i < n_blocks && alive; i++) {
+        int n = 0;                                        // blocks this tile has processed
+        for (int i = lo_t[t]; i < hi_t[t] && alive; i++, n++) {
             const int key0 = (jb0 + i) * FT_BN;
             const int buf = i & 1;
-            alive = bar_wait(s_full, i & 1, err);
+            alive = bar_wait(s_full0 + 8 * t, n & 1, err);
             if (!alive) break;
             fence_after();
             const bool need_mask = (key0 + FT_BN - 1 > first_pos) || (window > 0);
@@ -287,10 +322,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
 #pragma unroll
                 for (int c = 0; c < 32; c++) ps[c & 3] += v[c];
-                const unsigned row_addr = p_s + (c0 >> 6) * ATOM_BYTES + r * 128;
+                const unsigned row_addr = p_s + t * P_TILE + r * 128;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; q4++) {     // four 16-byte chunks of 8 keys
-                    const int chunk = ((c0 & 63) >> 3) + q4;
+                    const int chunk = (c0 >> 3) + q4;
                     uint4 u;
                     __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&u);
 #pragma unroll
@@ -301,15 +336,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
             l_run = l_run * corr + psum;
-            // the last block may hold positions beyond the sequence: whatever the cache has there
-            // must not reach the product (0 x NaN), so those rows of V are cleared
-            if (key0 + FT_BN - 1 > last_pos) {
+            // the block's last ring block may hold positions beyond the sequence: whatever the cache
+            // has there must not reach the product (0 x NaN), so those rows of V are cleared (by
+            // every tile that uses the block: the writes are the same)
+            if (key0 + FT_BN - 1 > cta_last_pos) {
                 alive = bar_wait(kv_full0 + 8 * buf, (i >> 1) & 1, err);
                 const int key = key0 + r;
-                if (key > last_pos) {
+                if (r < FT_BN && key > cta_last_pos) {
 #pragma unroll
                     for (int a = 0; a < NA; a++) {
-                        const unsigned row_addr = v_s + buf * KV_BYTES + a * ATOM_BYTES + r * 128;
+                        const unsigned row_addr = v_s + buf * KV_BYTES + a * KV_ATOM + r * 128;
 #pragma unroll
                         for (int q8 = 0; q8 < 8; q8++)
                             asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(row_addr + q8 * 16), "r"(0u) : "memory");
@@ -318,9 +354,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             fence_before();
-            bar_arrive(p_full);
+            bar_arrive(p_full0 + 8 * t);
             // O = O * corr + P V
-            alive = alive && bar_wait(o_full, i & 1, err);
+            alive = alive && bar_wait(o_full0 + 8 * t, n & 1, err);
             if (!alive) break;
             fence_after();
 #pragma unroll
@@ -331,9 +367,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (int c = 0; c < 32; c++) o_reg[c0 + c] = fmaf(o_reg[c0 + c], corr, v[c]);
             }
         }
-        if (alive && r < rows_here) {
+        if (alive && r < rows_t[t]) {
             const float inv = 1.0f / l_run;
-            bf16* dst = out + ((size_t)(q0 + row0 + r) * nh + h) * D;
+            bf16* dst = out + ((size_t)(q0 + cta_row0 + t * FT_BM + r) * nh + h) * D;
 #pragma unroll
             for (int c = 0; c < D; c += 8) {
                 float f[8];
@@ -345,7 +381,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == FT_MMA_WARP) {
         fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
@@ -383,7 +419,7 @@ static int ft_make_map(CUtensorMap* map, const void* ptr, long long rows, long l
     return r == CUDA_SUCCESS ? 0 : ILLM_ERR_BAD_ARG;
 }
 
-template <int D>
+template <int D, int TILES>
 static int ft_launch(const void* q, int q_stride, int T, const void* kc, const void* vc, long long n_pages,
                      const int* block_table, int max_pages, const int* cu_q, const int* seq_lens, void* out, int B,
                      int max_q, int nh, int nkv, int page_size, int window, float scale, int* err, cudaStream_t s) {
@@ -391,16 +427,31 @@ static int ft_launch(const void* q, int q_stride, int T, const void* kc, const v
     int rc;
     if ((rc = ft_make_map(&mq, q, T, (long long)nh * D, q_stride, FT_BM)) != 0) return rc;
     const long long kv_rows = n_pages * nkv * page_size;
-    if ((rc = ft_make_map(&mk, kc, kv_rows, D, D, 64)) != 0) return rc;
-    if ((rc = ft_make_map(&mv, vc, kv_rows, D, D, 64)) != 0) return rc;
-    const size_t smem = (size_t)FT_BM * D * 2 + 4 * (size_t)FT_BN * D * 2 + (size_t)FT_BM * FT_BN * 2 + 1024;
-    auto kern = attention_prefill_tc_kernel<D>;
+    if ((rc = ft_make_map(&mk, kc, kv_rows, D, D, FT_BN)) != 0) return rc;
+    if ((rc = ft_make_map(&mv, vc, kv_rows, D, D, FT_BN)) != 0) return rc;
+    const size_t smem = (size_t)TILES * FT_BM * D * 2 + 4 * (size_t)FT_BN * D * 2 +
+                        (size_t)TILES * FT_BM * FT_BN * 2 + 128;   // + barriers and the tensor-memory address
+    auto kern = attention_prefill_tc_kernel<D, TILES>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    dim3 grid((max_q + FT_BM - 1) / FT_BM, nh, B);
-    illm_launch(kern, grid, dim3(FT_THREADS), smem, s, mq, mk, mv, block_table, max_pages, cu_q, seq_lens,
+    dim3 grid((max_q + TILES * FT_BM - 1) / (TILES * FT_BM), nh, B);
+    illm_launch(kern, grid, dim3(FT_THREADS(TILES)), smem, s, mq, mk, mv, block_table, max_pages, cu_q, seq_lens,
                 (bf16*)out, nh, nkv, page_size, window, scale * 1.4426950408889634f, err);
     return illm_launch_status();
+}
+
+// Two query tiles per block when that still gives every SM several blocks; one tile otherwise
+// (short prompts: more, smaller blocks balance the causal triangle better).
+template <int D>
+static int ft_pick(const void* q, int q_stride, int T, const void* kc, const void* vc, long long n_pages,
+                   const int* block_table, int max_pages, const int* cu_q, const int* seq_lens, void* out, int B,
+                   int max_q, int nh, int nkv, int page_size, int window, float scale, int* err, cudaStream_t s) {
+    const long long blocks2 = (long long)((max_q + 2 * FT_BM - 1) / (2 * FT_BM)) * nh * B;
+    if (blocks2 >= 4 * 148)
+        return ft_launch<D, 2>(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q,
+                               nh, nkv, page_size, window, scale, err, s);
+    return ft_launch<D, 1>(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q,
+                           nh, nkv, page_size, window, scale, err, s);
 }
 
 // q: the packed projection [T, q_stride] whose first nh*d columns are the query heads;
@@ -416,10 +467,10 @@ extern "C" int illm_attention_prefill_tc(const void* q, int q_stride, int T, con
         return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     if (d == 128)
-        return ft_launch<128>(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q,
+        return ft_pick<128>(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q,
                               nh, nkv, page_size, window, scale, err, s);
     if (d == 64)
-        return ft_launch<64>(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q,
+        return ft_pick<64>(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q,
                              nh, nkv, page_size, window, scale, err, s);
     return ILLM_ERR_BAD_ARG;
 }
