@@ -320,7 +320,7 @@ extern "C" int illm_gemm_bf16_tc_tune(int stages) {
 
 template <typename TOut>
 static int run_tc(const void* X, const void* W, TOut* out, int M, int N, int K, float* ws, int splits, int* err,
-                  cudaStream_t s) {
+                  cudaStream_t s, int skip_reduce) {
     const int k_iters = (K + TC_BK - 1) / TC_BK;
     CUtensorMap ma, mb;
     int rc;
@@ -339,7 +339,7 @@ static int run_tc(const void* X, const void* W, TOut* out, int M, int N, int K, 
             if (bn == 16) rc = launch_tc<16, true, float>(ma, mb, ws, n, N, N, M, k_iters, splits, err, s);
             else if (bn == 32) rc = launch_tc<32, true, float>(ma, mb, ws, n, N, N, M, k_iters, splits, err, s);
             else rc = launch_tc<64, true, float>(ma, mb, ws, n, N, N, M, k_iters, splits, err, s);
-            if (rc != 0) return rc;
+            if (rc != 0 || skip_reduce) return rc;
             illm_launch(splitk_reduce_kernel<TOut>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, ws, out, n, splits);
             return illm_launch_status();
         }
@@ -359,13 +359,26 @@ static int run_tc(const void* X, const void* W, TOut* out, int M, int N, int K, 
 
 // out_dtype: ILLM_BF16 or ILLM_F32.  `ws`: float workspace of splits * M * N elements (splits > 1
 // is honoured for M <= 64 only).  X and W must be 16-byte aligned, K a multiple of 8.
+// skip_reduce != 0 (with splits > 1): the slices stay in `ws` for a consumer that adds them up itself
+// (illm_add_rmsnorm_partials, illm_rope_kv_write_partials) and `out` is not written.
 extern "C" int illm_gemm_bf16_tc(const void* X, const void* W, void* out, int out_dtype, int M, int N, int K,
-                                 float* ws, int splits, int* err, void* stream) {
+                                 float* ws, int splits, int* err, void* stream, int skip_reduce) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K & 7) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || splits < 1) return ILLM_ERR_BAD_ARG;
     if (splits > 1 && ws == nullptr) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_dtype == ILLM_BF16) return run_tc<bf16>(X, W, (bf16*)out, M, N, K, ws, splits, err, s);
-    if (out_dtype == ILLM_F32) return run_tc<float>(X, W, (float*)out, M, N, K, ws, splits, err, s);
+    if (out_dtype == ILLM_BF16) return run_tc<bf16>(X, W, (bf16*)out, M, N, K, ws, splits, err, s, skip_reduce);
+    if (out_dtype == ILLM_F32) return run_tc<float>(X, W, (float*)out, M, N, K, ws, splits, err, s, skip_reduce);
     return ILLM_ERR_BAD_ARG;
+}
+
+// out[i] = sum over slices (ascending) of ws[z][i]: the stand-alone form of the reduction.
+extern "C" int illm_splitk_reduce(const float* ws, void* out, int out_dtype, long long n, int splits, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (out_dtype == ILLM_BF16) illm_launch(splitk_reduce_kernel<bf16>, dim3(blocks), dim3(256), 0, s, ws, (bf16*)out, n, splits);
+    else if (out_dtype == ILLM_F32) illm_launch(splitk_reduce_kernel<float>, dim3(blocks), dim3(256), 0, s, ws, (float*)out, n, splits);
+    else return ILLM_ERR_BAD_ARG;
+    return illm_launch_status();
 }

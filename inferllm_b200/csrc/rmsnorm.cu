@@ -46,7 +46,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restri
 template <typename TA, typename TW, int ITERS>
 __global__ void __launch_bounds__(RN_THREADS)
 add_rmsnorm_reg_kernel(float* __restrict__ resid, const TA* __restrict__ delta, const TW* __restrict__ w,
-                       TA* __restrict__ y, const int* __restrict__ rows, int H, float eps, int write_resid) {
+                       TA* __restrict__ y, const int* __restrict__ rows, int H, float eps, int write_resid,
+                       const float* __restrict__ partials, int splits, long long split_stride) {
     pdl_grid_sync();
     __shared__ float scratch[32];
     const int r = rows ? rows[blockIdx.x] : blockIdx.x;
@@ -62,6 +63,19 @@ add_rmsnorm_reg_kernel(float* __restrict__ resid, const TA* __restrict__ delta, 
             if (dl) {
                 float d8[8];
                 load8(dl + c, d8);
+#pragma unroll
+                for (int k = 0; k < 8; k++) v[i][k] += d8[k];
+                if (write_resid) store8(x + c, v[i]);
+            } else if (partials) {
+                // the addend is still in K slices (float32, from a split matrix product): they are
+                // summed here, in ascending order, instead of by a kernel of their own
+                float d8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (int z = 0; z < splits; z++) {
+                    float p8[8];
+                    load8(partials + (size_t)z * split_stride + (size_t)r * H + c, p8);
+#pragma unroll
+                    for (int k = 0; k < 8; k++) d8[k] += p8[k];
+                }
 #pragma unroll
                 for (int k = 0; k < 8; k++) v[i][k] += d8[k];
                 if (write_resid) store8(x + c, v[i]);
@@ -88,12 +102,14 @@ add_rmsnorm_reg_kernel(float* __restrict__ resid, const TA* __restrict__ delta, 
 
 template <typename TA, typename TW>
 static int launch(float* resid, const void* delta, const void* w, void* y, const int* rows,
-                  int n_rows, int H, float eps, int write_resid, cudaStream_t s) {
+                  int n_rows, int H, float eps, int write_resid, cudaStream_t s,
+                  const float* partials = nullptr, int splits = 0, long long split_stride = 0) {
+    if (partials && !((H & 7) == 0 && H <= 8 * 8 * RN_THREADS)) return ILLM_ERR_BAD_ARG;
     if ((H & 7) == 0 && H <= 8 * 8 * RN_THREADS) {
         const int iters = (H / 8 + RN_THREADS - 1) / RN_THREADS;
 #define RN_CASE(N)                                                                                   \
     illm_launch(add_rmsnorm_reg_kernel<TA, TW, N>, dim3(n_rows), dim3(RN_THREADS), 0, s, resid, (const TA*)delta, (const TW*)w, \
-                                                                   (TA*)y, rows, H, eps, write_resid)
+                                                                   (TA*)y, rows, H, eps, write_resid, partials, splits, split_stride)
         if (iters <= 1) RN_CASE(1);
         else if (iters <= 2) RN_CASE(2);
         else if (iters <= 4) RN_CASE(4);
@@ -127,6 +143,21 @@ extern "C" int illm_add_rmsnorm(float* resid, const void* delta, const void* w, 
         return launch<float, float>(resid, delta, w, y, rows, n_rows, H, eps, write_resid, s);
     if (act_dtype == ILLM_F32 && w_dtype == ILLM_BF16)
         return launch<float, bf16>(resid, delta, w, y, rows, n_rows, H, eps, write_resid, s);
+    return ILLM_ERR_BAD_ARG;
+}
+
+// The same with the addend given as `splits` float32 slices [splits][rows][H] of a split-K matrix
+// product (slice z at partials + z * split_stride): saves the kernel that would add them up.
+extern "C" int illm_add_rmsnorm_partials(float* resid, const float* partials, int splits, long long split_stride,
+                                         const void* w, int w_dtype, void* y, int act_dtype, const int* rows,
+                                         int n_rows, int H, float eps, int write_resid, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (!partials || splits < 1) return ILLM_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == ILLM_BF16 && w_dtype == ILLM_BF16)
+        return launch<bf16, bf16>(resid, nullptr, w, y, rows, n_rows, H, eps, write_resid, s, partials, splits, split_stride);
+    if (act_dtype == ILLM_BF16 && w_dtype == ILLM_F32)
+        return launch<bf16, float>(resid, nullptr, w, y, rows, n_rows, H, eps, write_resid, s, partials, splits, split_stride);
     return ILLM_ERR_BAD_ARG;
 }
 

@@ -24,7 +24,8 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const float2* __restr
                                      const int* __restrict__ block_table, int max_pages,
                                      TA* __restrict__ kc, TA* __restrict__ vc, int nh, int nkv, int d,
                                      int rot, int page_size, int write_kv, int table_positions,
-                                     int* __restrict__ err) {
+                                     int* __restrict__ err, const float* __restrict__ partials, int splits,
+                                     long long split_stride) {
     pdl_grid_sync();
     const int t = blockIdx.x;
     const int p = token_pos[t];
@@ -60,6 +61,25 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const float2* __restr
     const bool vec = ((half & 7) == 0) && ((d & 7) == 0) && ((rot & 7) == 0);
     if (vec) {
         const int cpd = d >> 3, hc = half >> 3;      // chunks per head, chunks per rotated half
+        // the projection may still be in K slices (float32, from a split matrix product): a chunk
+        // is then the sum of its slices in ascending order, and Q is written to `qkv` for the
+        // attention kernel while K and V go to the cache only
+        const size_t row_off = (size_t)t * (nh + 2 * nkv) * d;
+        auto fetch = [&](const TA* src_elem, float* out8) {
+            if (partials) {
+                const size_t off = row_off + (size_t)(src_elem - row);
+#pragma unroll
+                for (int k = 0; k < 8; k++) out8[k] = 0.f;
+                for (int z = 0; z < splits; z++) {
+                    float p8[8];
+                    load8(partials + (size_t)z * split_stride + off, p8);
+#pragma unroll
+                    for (int k = 0; k < 8; k++) out8[k] += p8[k];
+                }
+            } else {
+                load8(src_elem, out8);
+            }
+        };
         for (int idx = lane; idx < (s1 - s0) * cpd; idx += 32) {
             const int slot = s0 + idx / cpd, c = idx % cpd;
             TA* src = row + (size_t)slot * d;
@@ -70,8 +90,8 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const float2* __restr
                 if (c < hc) {
                     const int j = c * 8;
                     float a[8], b[8], ra[8], rb[8];
-                    load8(src + j, a);
-                    load8(src + j + half, b);
+                    fetch(src + j, a);
+                    fetch(src + j + half, b);
 #pragma unroll
                     for (int k = 0; k < 8; k++) {
                         const float2 cs2 = cst[j + k];
@@ -82,13 +102,13 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const float2* __restr
                     store8(dst + j + half, rb);
                 } else if (c >= 2 * hc && is_k) {       // K channels outside the rotated part
                     float a[8];
-                    load8(src + c * 8, a);
+                    fetch(src + c * 8, a);
                     store8(dst + c * 8, a);
                 }
             } else if (write_kv) {
                 TA* dst = vdst + (size_t)(slot - nh - nkv) * head_stride;
                 float a[8];
-                load8(src + c * 8, a);
+                fetch(src + c * 8, a);
                 store8(dst + c * 8, a);
             }
         }
@@ -145,11 +165,37 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const float2* __restr
     }
 }
 
+static int rope_launch(void* qkv, const float* cos_sin, const int* token_pos, const int* token_seq,
+                       const int* block_table, int max_pages, void* kc, void* vc, int act_dtype, int T, int nh,
+                       int nkv, int d, int rot, int page_size, int write_kv, int table_positions, int* err,
+                       void* stream, const float* partials, int splits, long long split_stride);
+
 extern "C" int illm_rope_kv_write(void* qkv, const float* cos_sin, const int* token_pos,
                                   const int* token_seq, const int* block_table, int max_pages,
                                   void* kc, void* vc, int act_dtype, int T, int nh, int nkv, int d,
                                   int rot, int page_size, int write_kv, int table_positions,
                                   int* err, void* stream) {
+    return rope_launch(qkv, cos_sin, token_pos, token_seq, block_table, max_pages, kc, vc, act_dtype, T, nh, nkv, d,
+                       rot, page_size, write_kv, table_positions, err, stream, nullptr, 0, 0);
+}
+
+// The same with the packed projection given as `splits` float32 slices [splits][T][(nh+2nkv)*d] of a
+// split-K matrix product; `qkv` receives the rotated Q heads (its K and V columns stay unwritten).
+// Needs the 16-byte path: d, rot and rot/2 multiples of 8.
+extern "C" int illm_rope_kv_write_partials(void* qkv, const float* partials, int splits, long long split_stride,
+                                           const float* cos_sin, const int* token_pos, const int* token_seq,
+                                           const int* block_table, int max_pages, void* kc, void* vc,
+                                           int act_dtype, int T, int nh, int nkv, int d, int rot, int page_size,
+                                           int write_kv, int table_positions, int* err, void* stream) {
+    if (!partials || splits < 1 || (d & 7) || (rot & 15)) return ILLM_ERR_BAD_ARG;
+    return rope_launch(qkv, cos_sin, token_pos, token_seq, block_table, max_pages, kc, vc, act_dtype, T, nh, nkv, d,
+                       rot, page_size, write_kv, table_positions, err, stream, partials, splits, split_stride);
+}
+
+static int rope_launch(void* qkv, const float* cos_sin, const int* token_pos, const int* token_seq,
+                       const int* block_table, int max_pages, void* kc, void* vc, int act_dtype, int T, int nh,
+                       int nkv, int d, int rot, int page_size, int write_kv, int table_positions, int* err,
+                       void* stream, const float* partials, int splits, long long split_stride) {
     if (T <= 0) return 0;
     if (rot < 0 || rot > d || (rot & 1) || (rot > 0 && cos_sin == nullptr)) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
@@ -159,11 +205,13 @@ extern "C" int illm_rope_kv_write(void* qkv, const float* cos_sin, const int* to
     if (act_dtype == ILLM_BF16)
         illm_launch(rope_kv_write_kernel<bf16>, dim3(grid), dim3(threads), 0, s, 
             (bf16*)qkv, (const float2*)cos_sin, token_pos, token_seq, block_table, max_pages,
-            (bf16*)kc, (bf16*)vc, nh, nkv, d, rot, page_size, write_kv, table_positions, err);
+            (bf16*)kc, (bf16*)vc, nh, nkv, d, rot, page_size, write_kv, table_positions, err, partials, splits,
+            split_stride);
     else if (act_dtype == ILLM_F32)
         illm_launch(rope_kv_write_kernel<float>, dim3(grid), dim3(threads), 0, s, 
             (float*)qkv, (const float2*)cos_sin, token_pos, token_seq, block_table, max_pages,
-            (float*)kc, (float*)vc, nh, nkv, d, rot, page_size, write_kv, table_positions, err);
+            (float*)kc, (float*)vc, nh, nkv, d, rot, page_size, write_kv, table_positions, err, partials, splits,
+            split_stride);
     else
         return ILLM_ERR_BAD_ARG;
     return illm_launch_status();

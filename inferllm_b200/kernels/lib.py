@@ -24,7 +24,10 @@ _SIGNATURES = {
     "illm_attention_decode": [P, I, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
     "illm_attention_decode_supported": [I, I, I],
     "illm_attention_prefill": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],
-    "illm_gemm_bf16_tc": [P, P, P, I, I, I, I, P, I, P, P],
+    "illm_gemm_bf16_tc": [P, P, P, I, I, I, I, P, I, P, P, I],
+    "illm_splitk_reduce": [P, P, I, LL, I, P],
+    "illm_add_rmsnorm_partials": [P, P, I, LL, P, I, P, I, P, I, I, F, I, P],
+    "illm_rope_kv_write_partials": [P, P, I, LL, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, P, P],
     "illm_gemm_bf16_tc_tune": [I],
     "illm_set_pdl": [I],
     "illm_attention_prefill_tc": [P, I, I, P, P, LL, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P],

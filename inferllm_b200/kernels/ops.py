@@ -88,6 +88,12 @@ def add_rmsnorm(resid, delta, weight, eps, out_dtype, rows=None, write_resid=Tru
     if H > MAX_NORM_WIDTH:
         raise KernelError(f"rmsnorm: width {H} exceeds the {MAX_NORM_WIDTH} that one block's "
                           "shared memory holds")
+    partials = None
+    if isinstance(delta, SplitKPartials):
+        if out_dtype == torch.bfloat16 and H % 8 == 0 and H <= 16384 and tuple(delta.shape) == tuple(resid.shape):
+            partials, delta = delta, None
+        else:
+            delta = delta.materialize(out_dtype)
     if delta is not None:
         _need(delta, "delta", out_dtype, 2)
         if delta.shape != resid.shape:
@@ -99,6 +105,12 @@ def add_rmsnorm(resid, delta, weight, eps, out_dtype, rows=None, write_resid=Tru
     if rows is not None:
         _need(rows, "rows", torch.int32, 1)
     y = torch.empty((n, H), dtype=out_dtype, device=resid.device)
+    if partials is not None:
+        _check(load().illm_add_rmsnorm_partials(
+            _ptr(resid), _ptr(partials.ws), partials.splits, partials.rows * partials.cols, _ptr(weight),
+            act_code(weight.dtype), _ptr(y), act_code(out_dtype), _ptr(rows), n, H, float(eps),
+            1 if write_resid else 0, _stream()), "add_rmsnorm_partials")
+        return y
     _check(load().illm_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(weight), act_code(weight.dtype),
                                    _ptr(y), act_code(out_dtype), _ptr(rows), n, H, float(eps),
                                    1 if write_resid else 0, _stream()), "add_rmsnorm")
@@ -106,6 +118,8 @@ def add_rmsnorm(resid, delta, weight, eps, out_dtype, rows=None, write_resid=Tru
 
 
 def residual_add(resid, delta):
+    if isinstance(delta, SplitKPartials):
+        delta = delta.materialize(torch.bfloat16)
     _need(resid, "resid", torch.float32)
     _need(delta, "delta")
     if delta.shape != resid.shape:
@@ -126,7 +140,16 @@ def swiglu(gu):
 def rope_kv_write(qkv, cos_sin, rot_dim, token_pos, token_seq, block_table, k_cache, v_cache,
                   n_heads, n_kv_heads, head_dim, page_size, write_kv, err):
     """Rotate Q (and K) of the packed projection in place and store K, V in the cache pages.
-    `cos_sin` float32 [positions, rot_dim/2, 2] or None with rot_dim 0."""
+    `cos_sin` float32 [positions, rot_dim/2, 2] or None with rot_dim 0.  Returns the tensor whose
+    first n_heads*head_dim columns hold the rotated queries: `qkv` itself, or, if `qkv` came as
+    `SplitKPartials`, a new tensor (the slices are added up on the way)."""
+    partials = None
+    if isinstance(qkv, SplitKPartials):
+        if head_dim % 8 == 0 and rot_dim % 16 == 0 and k_cache is not None and k_cache.dtype == torch.bfloat16:
+            partials = qkv
+            qkv = torch.empty(partials.shape, dtype=torch.bfloat16, device=partials.device)
+        else:
+            qkv = qkv.materialize(torch.bfloat16)
     _need(qkv, "qkv", None, 2)
     T = qkv.shape[0]
     if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim:
@@ -146,11 +169,20 @@ def rope_kv_write(qkv, cos_sin, rot_dim, token_pos, token_seq, block_table, k_ca
         if cos_sin.shape[1] != rot_dim // 2:
             raise KernelError("cos_sin table does not match rot_dim")
         n_pos = cos_sin.shape[0]
+    if partials is not None:
+        _check(load().illm_rope_kv_write_partials(
+            _ptr(qkv), _ptr(partials.ws), partials.splits, partials.rows * partials.cols,
+            _ptr(cos_sin) if rot_dim else None, _ptr(token_pos), _ptr(token_seq), _ptr(block_table),
+            block_table.shape[1], _ptr(k_cache) if write_kv else None, _ptr(v_cache) if write_kv else None,
+            act_code(qkv.dtype), T, n_heads, n_kv_heads, head_dim, rot_dim, page_size, 1 if write_kv else 0,
+            n_pos, _ptr(err), _stream()), "rope_kv_write_partials")
+        return qkv
     _check(load().illm_rope_kv_write(
         _ptr(qkv), _ptr(cos_sin) if rot_dim else None, _ptr(token_pos), _ptr(token_seq),
         _ptr(block_table), block_table.shape[1], _ptr(k_cache) if write_kv else None,
         _ptr(v_cache) if write_kv else None, act_code(qkv.dtype), T, n_heads, n_kv_heads, head_dim,
         rot_dim, page_size, 1 if write_kv else 0, n_pos, _ptr(err), _stream()), "rope_kv_write")
+    return qkv
 
 
 def attention_generic(qkv, k_cache, v_cache, block_table, token_pos, token_seq, n_heads,
@@ -297,6 +329,25 @@ def tc_error_word(device):
     return _tc_err[key]
 
 
+class SplitKPartials:
+    """The K slices of a split matrix product that have not been added up yet: float32
+    [splits, M, N].  `add_rmsnorm` and `rope_kv_write` take it in place of the finished tensor
+    and do the addition themselves (ascending order of the slice, as the stand-alone reduction
+    does), which saves a kernel per product in a decode step; `materialize` is for everyone else."""
+
+    def __init__(self, ws: torch.Tensor):
+        self.ws = ws
+        self.splits, self.rows, self.cols = ws.shape
+        self.shape = (self.rows, self.cols)
+        self.device = ws.device
+
+    def materialize(self, dtype=torch.bfloat16) -> torch.Tensor:
+        out = torch.empty(self.shape, dtype=dtype, device=self.device)
+        _check(load().illm_splitk_reduce(_ptr(self.ws), _ptr(out), act_code(dtype), self.rows * self.cols,
+                                         self.splits, _stream()), "splitk_reduce")
+        return out
+
+
 def gemm_tc_splits(M, N, K):
     """How many slices of K a decode-sized product (M <= 64) is cut into, so that about two
     blocks per SM stream the weights; 1 for larger M."""
@@ -304,11 +355,15 @@ def gemm_tc_splits(M, N, K):
         return 1
     tiles = -(-N // 128)
     k_iters = -(-K // 64)
-    return max(1, min(2 * N_SMS // tiles, k_iters // 8))
+    splits = max(1, min(2 * N_SMS // tiles, k_iters // 8))
+    per = -(-k_iters // splits)
+    return -(-k_iters // per)          # every slice owns at least one 64-wide piece of K
 
 
-def gemm_bf16_tc(x, w, out_dtype=torch.bfloat16, splits=None):
-    """bfloat16 x [M, K] . w [N, K]^T on tcgen05 tensor cores, float32 accumulation."""
+def gemm_bf16_tc(x, w, out_dtype=torch.bfloat16, splits=None, defer_reduce=False):
+    """bfloat16 x [M, K] . w [N, K]^T on tcgen05 tensor cores, float32 accumulation.
+    `defer_reduce`: if the product is split over K, return its slices as `SplitKPartials`
+    instead of adding them up."""
     _need(x, "x", torch.bfloat16, 2)
     _need(w, "w", torch.bfloat16, 2)
     M, K = x.shape
@@ -320,10 +375,18 @@ def gemm_bf16_tc(x, w, out_dtype=torch.bfloat16, splits=None):
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     if splits is None:
         splits = gemm_tc_splits(M, N, K)
+    else:
+        k_iters = -(-K // 64)
+        splits = max(1, min(int(splits), k_iters))
+        splits = -(-k_iters // -(-k_iters // splits))
+    if M > 64:
+        splits = 1
     ws = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
+    defer = bool(defer_reduce and splits > 1)
     _check(load().illm_gemm_bf16_tc(_ptr(x), _ptr(w), _ptr(out), act_code(out_dtype), M, N, K, _ptr(ws),
-                                    splits, _ptr(tc_error_word(x.device)), _stream()), "gemm_bf16_tc")
-    return out
+                                    splits, _ptr(tc_error_word(x.device)), _stream(), 1 if defer else 0),
+           "gemm_bf16_tc")
+    return SplitKPartials(ws) if defer else out
 
 
 def set_pdl(on: bool) -> None:
@@ -348,8 +411,9 @@ def set_gemm_backend(name: str) -> None:
     _GEMM_BACKEND = name
 
 
-def linear(x, w, out_dtype=None):
-    """x [M, K] . w [N, K]^T.  float32: the package's own FMA kernel.  bfloat16: the library
+def linear(x, w, out_dtype=None, defer_reduce=False):
+    """x [M, K] . w [N, K]^T.  `defer_reduce=True` allows the result to come back as
+    `SplitKPartials` (only a caller that hands it to `add_rmsnorm` or `rope_kv_write` asks).  float32: the package's own FMA kernel.  bfloat16: the library
     product with float32 accumulation, rounded to bfloat16 or kept float32 (`out_dtype`)."""
     if x.dtype == torch.float32:
         return gemm_f32(x, w)
@@ -358,7 +422,7 @@ def linear(x, w, out_dtype=None):
     M, K = x.shape
     if M > 0 and K % 8 == 0 and (_GEMM_BACKEND == "tc" or (
             _GEMM_BACKEND == "auto" and M <= GEMM_TC_MAX_TOKENS_AUTO)):
-        return gemm_bf16_tc(x, w, out_dtype or torch.bfloat16)
+        return gemm_bf16_tc(x, w, out_dtype or torch.bfloat16, defer_reduce=defer_reduce)
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     return torch.mm(x, w.t())

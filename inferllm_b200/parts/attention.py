@@ -57,9 +57,16 @@ class Attention(Mixer):
         return PagedKV(self.n_kv_heads, self.head_dim, self.window)
 
     def forward(self, h, ctx, cache, writes):
-        qkv = ops.linear(h, self.w_qkv)
+        return self._run(h, ctx, cache, False)
+
+    def forward_deferred(self, h, ctx, cache, writes):
+        return self._run(h, ctx, cache, True)
+
+    def _run(self, h, ctx, cache, defer_output):
+        # the packed projection may stay in K slices: the rotation kernel adds them up
+        qkv = ops.linear(h, self.w_qkv, defer_reduce=True)
         geometry = (self.n_heads, self.n_kv_heads, self.head_dim)
-        self.position.encode_and_store(qkv, geometry, ctx, cache)
+        qkv = self.position.encode_and_store(qkv, geometry, ctx, cache)
         o = ops.attention(qkv, cache, ctx, self.n_heads, self.n_kv_heads, self.head_dim,
                           self.window, self.scale)
-        return ops.linear(o, self.w_o)
+        return ops.linear(o, self.w_o, defer_reduce=defer_output)

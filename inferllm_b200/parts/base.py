@@ -94,9 +94,11 @@ class PositionEncoding(Part):
     def prepare(self) -> None:
         """Build device tables; called once after construction on a device."""
 
-    def encode_and_store(self, qkv, geometry, ctx, kv) -> None:
-        """Encode positions into the Q and K heads of the packed projection `qkv` in place
-        and, if `kv` is given, store the new K and V in the cache."""
+    def encode_and_store(self, qkv, geometry, ctx, kv):
+        """Encode positions into the Q and K heads of the packed projection `qkv` and store the
+        new K and V in the cache (if `kv.writes`).  Returns the tensor that holds the encoded
+        queries in its first heads * head_dim columns: `qkv` itself (encoded in place) or, when
+        `qkv` arrived as unreduced slices of a split matrix product, a new tensor."""
         raise NotImplementedError
 
 
@@ -116,10 +118,20 @@ class Mixer(Part):
         storage for the step (a `KVView`, a `StateView` or None)."""
         raise NotImplementedError
 
+    def forward_deferred(self, h, ctx, cache, writes):
+        """Like `forward`, but the result may be the unreduced slices of a split matrix product
+        (`kernels.ops.SplitKPartials`), for a caller that only adds it to the residual stream
+        (`ResidualStream.add` takes both).  By default the same as `forward`."""
+        return self.forward(h, ctx, cache, writes)
+
 
 class FeedForward(Part):
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError
+
+    def forward_deferred(self, h, ctx):
+        """See `Mixer.forward_deferred`."""
+        return self.forward(h, ctx)
 
 
 class Block:
@@ -144,9 +156,11 @@ class ResidualStream:
 
     def __init__(self, x: torch.Tensor):
         self.x = x
-        self.pending: Optional[torch.Tensor] = None
+        self.pending = None     # a tensor [T, H], or kernels.ops.SplitKPartials of that shape
 
-    def add(self, delta: torch.Tensor) -> None:
+    def add(self, delta) -> None:
+        """`delta`: a tensor in the compute dtype, or the unreduced slices of a split matrix
+        product; `ops.add_rmsnorm` and `ops.residual_add` take either."""
         if self.pending is not None:
             self.flush()
         self.pending = delta

@@ -16,7 +16,9 @@ class PreNormBlock(Block):
         return ("norm1", "norm2")
 
     def forward(self, stream, ctx, cache, writes):
+        # the outputs only go into the residual stream, so they may stay unreduced (see
+        # Mixer.forward_deferred): the next norm adds the slices while it reads the row anyway
         h = self.norms["norm1"].forward(stream)
-        stream.add(self.mixer.forward(h, ctx, cache, writes))
+        stream.add(self.mixer.forward_deferred(h, ctx, cache, writes))
         h = self.norms["norm2"].forward(stream)
-        stream.add(self.ffn.forward(h, ctx))
+        stream.add(self.ffn.forward_deferred(h, ctx))

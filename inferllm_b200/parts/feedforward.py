@@ -39,3 +39,7 @@ class GatedMLP(FeedForward):
     def forward(self, h, ctx):
         gu = ops.linear(h, self.w_gate_up)
         return ops.linear(ops.swiglu(gu), self.w_down)
+
+    def forward_deferred(self, h, ctx):
+        gu = ops.linear(h, self.w_gate_up)
+        return ops.linear(ops.swiglu(gu), self.w_down, defer_reduce=True)

@@ -40,9 +40,9 @@ class RopeHalf(PositionEncoding):
 
     def encode_and_store(self, qkv, geometry, ctx, kv):
         n_heads, n_kv_heads, head_dim = geometry
-        ops.rope_kv_write(qkv, self.table, self.rot_dim, ctx.token_pos, ctx.token_seq,
-                          kv.block_table, kv.k if kv.writes else None, kv.v if kv.writes else None,
-                          n_heads, n_kv_heads, head_dim, kv.page_size, kv.writes, ctx.err)
+        return ops.rope_kv_write(qkv, self.table, self.rot_dim, ctx.token_pos, ctx.token_seq,
+                                 kv.block_table, kv.k if kv.writes else None, kv.v if kv.writes else None,
+                                 n_heads, n_kv_heads, head_dim, kv.page_size, kv.writes, ctx.err)
 
 
 @register_position("none")
@@ -50,5 +50,6 @@ class NoPosition(PositionEncoding):
     def encode_and_store(self, qkv, geometry, ctx, kv):
         n_heads, n_kv_heads, head_dim = geometry
         if kv.writes:
-            ops.rope_kv_write(qkv, None, 0, ctx.token_pos, ctx.token_seq, kv.block_table, kv.k, kv.v,
-                              n_heads, n_kv_heads, head_dim, kv.page_size, True, ctx.err)
+            return ops.rope_kv_write(qkv, None, 0, ctx.token_pos, ctx.token_seq, kv.block_table, kv.k, kv.v,
+                                     n_heads, n_kv_heads, head_dim, kv.page_size, True, ctx.err)
+        return qkv

@@ -163,6 +163,54 @@ def test_gemm_bf16_tc_rows_do_not_depend_on_the_batch():
         ops.gemm_bf16_tc(dev(x[:, :1020]), dev(w[:, :1020]))
 
 
+def test_unreduced_split_k_slices_feed_norm_and_rope():
+    """A decode-sized product may hand its K slices on unreduced: the norm and the rotation kernel
+    add them up themselves and must give what the finished tensor gives."""
+    g = torch.Generator().manual_seed(2)
+    M, H = 5, 1024
+    x, w = torch.randn(M, 4096, generator=g).bfloat16(), (torch.randn(H, 4096, generator=g) * 0.05).bfloat16()
+    part = ops.gemm_bf16_tc(dev(x), dev(w), defer_reduce=True)
+    assert isinstance(part, ops.SplitKPartials) and part.splits > 1 and part.shape == (M, H)
+    full = ops.gemm_bf16_tc(dev(x), dev(w), torch.float32)
+    assert torch.equal(part.materialize(torch.float32), full)      # same slices, same order
+    assert maxrel(f64(full), plain.linear(f64(x), f64(w))) <= 1e-4
+    resid = torch.randn(M, H, generator=g)
+    wn = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16()
+    r1, r2 = dev(resid), dev(resid)
+    y1 = ops.add_rmsnorm(r1, part, dev(wn), 1e-5, torch.bfloat16)
+    ref_x = f64(resid) + f64(full)
+    assert maxrel(f64(r1), ref_x) <= 1e-6 and maxrel(f64(y1), plain.rms_norm(ref_x, f64(wn), 1e-5)) <= 2 ** -8
+    rows = torch.tensor([4, 1], dtype=torch.int32)
+    y2 = ops.add_rmsnorm(r2, part, dev(wn), 1e-5, torch.bfloat16, rows=dev(rows), write_resid=False)
+    assert torch.equal(r2.cpu(), resid) and maxrel(f64(y2), plain.rms_norm(ref_x[[4, 1]], f64(wn), 1e-5)) <= 2 ** -8
+    r3 = dev(resid)
+    ops.residual_add(r3, part)
+    assert maxrel(f64(r3), ref_x) <= 2 ** -8 * np.abs(f64(full)).max()
+    # the packed projection of an attention layer: 3 heads + 2 x 1 kv heads of 64 channels
+    nh, nkv, d, page = 3, 1, 64, 16
+    wq = (torch.randn((nh + 2 * nkv) * d, 4096, generator=g) * 0.05).bfloat16()
+    part = ops.gemm_bf16_tc(dev(x), dev(wq), defer_reduce=True, splits=4)
+    qkv_full = part.materialize(torch.float32)
+    from inferllm_b200.config import PartSpec
+    from inferllm_b200.parts import Runtime, build_part
+    rope = build_part("position", PartSpec("rope_half", dict(head_dim=d, theta=1e4, max_positions=64)),
+                      Runtime(torch.device("cuda"), torch.bfloat16))
+    rope.prepare()
+    kc = torch.zeros(4, nkv, page, d, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    table = torch.tensor([[2, 0]], dtype=torch.int32).cuda()
+    pos = torch.tensor([3, 4, 5, 16, 17], dtype=torch.int32).cuda()
+    seq = torch.zeros(M, dtype=torch.int32).cuda()
+    out = ops.rope_kv_write(part, rope.table, d, pos, seq, table, kc, vc, nh, nkv, d, page, True, err_word())
+    src = f64(qkv_full).reshape(M, nh + 2 * nkv, d)
+    want = plain.rope_rotate_half(src[:, :nh + nkv], pos.cpu().numpy(), 1e4)
+    assert maxrel(f64(out).reshape(M, nh + 2 * nkv, d)[:, :nh], want[:, :nh]) <= 2 ** -8
+    for i, p_ in enumerate(pos.tolist()):
+        pg = int(table[0, p_ // page])
+        assert maxrel(f64(kc)[pg, :, p_ % page], want[i, nh:]) <= 2 ** -8
+        assert maxrel(f64(vc)[pg, :, p_ % page], src[i, nh + nkv:]) <= 2 ** -8
+
+
 # ---- rope + cache write, attention: a hand-made paged cache
 
 
