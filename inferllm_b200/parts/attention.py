@@ -63,8 +63,8 @@ class Attention(Mixer):
         return self._run(h, ctx, cache, True)
 
     def _run(self, h, ctx, cache, defer_output):
-        # the packed projection may stay in K slices: the rotation kernel adds them up
-        qkv = ops.linear(h, self.w_qkv, defer_reduce=True)
+        # the packed projection may stay in K slices if the position encoding's kernel adds them up
+        qkv = ops.linear(h, self.w_qkv, defer_reduce=self.position.takes_partials)
         geometry = (self.n_heads, self.n_kv_heads, self.head_dim)
         qkv = self.position.encode_and_store(qkv, geometry, ctx, cache)
         o = ops.attention(qkv, cache, ctx, self.n_heads, self.n_kv_heads, self.head_dim,

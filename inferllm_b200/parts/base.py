@@ -91,6 +91,11 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    # True: `encode_and_store` also takes the packed projection as unreduced slices of a split
+    # matrix product (`kernels.ops.SplitKPartials`) and adds them up itself.  False (default): it
+    # always gets a finished tensor.
+    takes_partials = False
+
     def prepare(self) -> None:
         """Build device tables; called once after construction on a device."""
 

@@ -20,6 +20,8 @@ from .base import PositionEncoding, register_position
 
 @register_position("rope_half")
 class RopeHalf(PositionEncoding):
+    takes_partials = True
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.head_dim = int(spec["head_dim"])
@@ -47,6 +49,8 @@ class RopeHalf(PositionEncoding):
 
 @register_position("none")
 class NoPosition(PositionEncoding):
+    takes_partials = True
+
     def encode_and_store(self, qkv, geometry, ctx, kv):
         n_heads, n_kv_heads, head_dim = geometry
         if kv.writes:
