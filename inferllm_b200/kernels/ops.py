@@ -394,6 +394,25 @@ def set_pdl(on: bool) -> None:
     load().illm_set_pdl(1 if on else 0)
 
 
+def gemm_bf16_tc2(x, w, out_dtype=torch.bfloat16, gated=False):
+    """bfloat16 x [M, K] . w [N, K]^T on pairs of SMs (tcgen05 cta_group::2), for prompts.
+    `gated`: w's rows come in blocks of 128 gate rows followed by their 128 up rows and the result
+    is silu(gate) * up, [M, N / 2]."""
+    _need(x, "x", torch.bfloat16, 2)
+    _need(w, "w", torch.bfloat16, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"gemm: x is [{M}, {K}] but w is {tuple(w.shape)}")
+    if K % 8 or x.data_ptr() % 16 or w.data_ptr() % 16 or (gated and N % 256):
+        raise KernelError(f"gemm_bf16_tc2: K = {K} must be a multiple of 8, the operands 16-byte aligned"
+                          " and a gated weight a multiple of 256 rows")
+    out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
+    _check(load().illm_gemm_bf16_tc2(_ptr(x), _ptr(w), _ptr(out), act_code(out_dtype), 1 if gated else 0, M, N, K,
+                                     _ptr(tc_error_word(x.device)), _stream()), "gemm_bf16_tc2")
+    return out
+
+
 _GEMM_BACKEND = "auto"
 GEMM_TC_MAX_TOKENS_AUTO = 16
 

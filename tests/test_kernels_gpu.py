@@ -152,6 +152,34 @@ def test_gemm_bf16_tc(M, N, K, out):
     assert int(ops.tc_error_word(got.device).item()) == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(129, 256, 64), (256, 512, 128), (300, 520, 328), (2048, 1000, 200),
+                                   (1000, 4096, 4096), (65, 300, 72)])
+@pytest.mark.parametrize("out", ["bfloat16", "float32"])
+def test_gemm_bf16_tc2(M, N, K, out):
+    """The product on pairs of SMs: ragged token tiles, weight rows that are no multiple of the
+    tile or of its halves, a ragged last slice of K, more tiles than SM pairs."""
+    g = torch.Generator().manual_seed(M + N + K)
+    x, w = torch.randn(M, K, generator=g).bfloat16(), torch.randn(N, K, generator=g).bfloat16()
+    got = ops.gemm_bf16_tc2(dev(x), dev(w), DT[out])
+    assert got.dtype == DT[out] and tuple(got.shape) == (M, N)
+    assert int(ops.tc_error_word(got.device).item()) == 0
+    ref = plain.linear(f64(x), f64(w))
+    assert maxrel(f64(got), ref) <= (2e-6 * math.sqrt(K) if out == "float32" else 2 ** -8)
+
+
+@pytest.mark.parametrize("M,I,K", [(300, 128, 64), (2048, 640, 328), (130, 11008, 256)])
+def test_gemm_bf16_tc2_gated(M, I, K):
+    """Gate and up rows interleaved in blocks of 128: the epilogue applies silu(gate) * up."""
+    g = torch.Generator().manual_seed(I)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    wg, wu = (torch.randn(I, K, generator=g) * 0.1).bfloat16(), (torch.randn(I, K, generator=g) * 0.1).bfloat16()
+    packed = torch.stack((wg.view(I // 128, 128, K), wu.view(I // 128, 128, K)), dim=1).reshape(2 * I, K)
+    got = ops.gemm_bf16_tc2(dev(x), dev(packed), torch.bfloat16, gated=True)
+    assert tuple(got.shape) == (M, I) and int(ops.tc_error_word(got.device).item()) == 0
+    ref = plain.silu(plain.linear(f64(x), f64(wg))) * plain.linear(f64(x), f64(wu))
+    assert maxrel(f64(got), ref) <= 2 ** -7
+
+
 def test_gemm_bf16_tc_rows_do_not_depend_on_the_batch():
     g = torch.Generator().manual_seed(1)
     x, w = torch.randn(40, 1024, generator=g).bfloat16(), torch.randn(512, 1024, generator=g).bfloat16()
