@@ -29,6 +29,17 @@ CONFIG_7B = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidde
                  num_attention_heads=32, num_key_value_heads=32, head_dim=128,
                  intermediate_size=11008, vocab_size=32000, rope_theta=10000.0, rms_norm_eps=1e-5,
                  max_position_embeddings=4096, tie_word_embeddings=False)
+# BASELINE.json configs[3] and configs[4], for runs beside the default one (--model 8b / 13b)
+CONFIG_8B = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidden_layers=32,
+                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336,
+                 vocab_size=128256, rope_theta=500000.0, rms_norm_eps=1e-5, max_position_embeddings=8192,
+                 tie_word_embeddings=False)
+CONFIG_13B = dict(architectures=["LlamaForCausalLM"], hidden_size=5120, num_hidden_layers=40,
+                  num_attention_heads=40, num_key_value_heads=40, head_dim=128, intermediate_size=13824,
+                  vocab_size=32000, rope_theta=10000.0, rms_norm_eps=1e-5, max_position_embeddings=4096,
+                  tie_word_embeddings=False)
+MODELS = {"7b": ("LLaMA-2-7B size", CONFIG_7B), "8b": ("Llama-3-8B size", CONFIG_8B),
+          "13b": ("LLaMA-2-13B size", CONFIG_13B)}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -127,6 +138,7 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--only", choices=["decode", "prefill"], help="run one scenario (for profiling); "
                     "prints a short JSON line of that scenario only")
+    ap.add_argument("--model", default="7b", choices=sorted(MODELS), help="sizes of BASELINE.json configs[2..4]")
     ap.add_argument("--gemm", default="auto", choices=["auto", "tc", "library"])
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels without programmatic dependent launch")
     ap.add_argument("--context", type=int, default=CONTEXT, help="position at which the timed decode steps end")
@@ -147,7 +159,8 @@ def main():
     from inferllm_b200 import Model, ModelConfig, StepItem, config_from_dict
     from inferllm_b200.kernels import ops
 
-    cfgd = dict(CONFIG_7B)
+    model_name, base_cfg = MODELS[args.model]
+    cfgd = dict(base_cfg)
     full_layers = cfgd["num_hidden_layers"]
     if args.layers:
         cfgd["num_hidden_layers"] = args.layers
@@ -227,6 +240,7 @@ def main():
     pf_flops = prefill_flops(cfgd, L, PREFILL_TOKENS, fig)
     prefill = {"value": round(PREFILL_TOKENS / pf_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
                "frac": round(pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               "frac_of_sustained": round(pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4),
                "tflops": round(pf_flops / (pf_ms * 1e-3) / 1e12, 1)}
 
     ms, launches, clocks = decode_run(B, CONTEXT, K, W)
@@ -264,7 +278,7 @@ def main():
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: uniform-random token ids, random-init weights N(0, 0.02)",
         "impl": "ours",
-        "config": {"model": "LLaMA-2-7B size", "global_batch": B, "seq_len": CONTEXT, "parallelism": "none (1 GPU)",
+        "config": {"model": model_name, "global_batch": B, "seq_len": CONTEXT, "parallelism": "none (1 GPU)",
                    "layers": L, "layers_of_config": full_layers, "hidden": cfgd["hidden_size"],
                    "heads": cfgd["num_attention_heads"], "kv_heads": cfgd["num_key_value_heads"],
                    "head_dim": cfgd["head_dim"], "intermediate": cfgd["intermediate_size"],

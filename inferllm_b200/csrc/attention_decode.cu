@@ -178,12 +178,12 @@ template <int D>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_acc,
                                               const float* __restrict__ part_ml,
                                               const int* __restrict__ token_pos, bf16* __restrict__ out,
-                                              int n_chunks, int nh, int window) {
+                                              int n_chunks, int nh, int window, int chunk_keys) {
     pdl_grid_sync();
     const int h = blockIdx.x, t = blockIdx.y, c = threadIdx.x;
     const int p = token_pos[t];
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-    const int cfirst = lo / AD_CHUNK, clast = p / AD_CHUNK;
+    const int cfirst = lo / chunk_keys, clast = p / chunk_keys;
     const size_t o = ((size_t)t * nh + h) * n_chunks;
     float M = -INFINITY;
     for (int ch = cfirst; ch <= clast; ch++) M = fmaxf(M, part_ml[(o + ch) * 2]);
@@ -206,7 +206,7 @@ static int launch(const void* q, int q_stride, const void* kc, const void* vc, c
         (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, block_table, max_pages, token_pos,
         token_seq, part_acc, part_ml, n_chunks, nh, nkv, page_size, window, scale * 1.4426950408889634f);
     illm_launch(attention_decode_merge_kernel<D>, dim3(dim3(nh, T)), dim3(D), 0, s, part_acc, part_ml, token_pos, (bf16*)out,
-                                                             n_chunks, nh, window);
+                                                             n_chunks, nh, window, AD_CHUNK);
     return illm_launch_status();
 }
 
@@ -229,6 +229,24 @@ extern "C" int illm_attention_decode(const void* q, int q_stride, const void* kc
     AD_CASE(64, 1) AD_CASE(64, 2) AD_CASE(64, 3) AD_CASE(64, 4) AD_CASE(64, 8)
 #undef AD_CASE
     return ILLM_ERR_BAD_ARG;
+}
+
+// The merge alone, for kernels that write the same partial layout with chunks of another size
+// (attention_decode_gqa.cu).
+extern "C" int illm_attention_decode_merge(const float* part_acc, const float* part_ml, const int* token_pos,
+                                           void* out, int T, int nh, int d, int n_chunks, int chunk_keys, int window,
+                                           void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (d == 128)
+        illm_launch(attention_decode_merge_kernel<128>, dim3(nh, T), dim3(128), 0, s, part_acc, part_ml, token_pos,
+                    (bf16*)out, n_chunks, nh, window, chunk_keys);
+    else if (d == 64)
+        illm_launch(attention_decode_merge_kernel<64>, dim3(nh, T), dim3(64), 0, s, part_acc, part_ml, token_pos,
+                    (bf16*)out, n_chunks, nh, window, chunk_keys);
+    else
+        return ILLM_ERR_BAD_ARG;
+    return illm_launch_status();
 }
 
 extern "C" int illm_attention_decode_supported(int d, int g, int page_size) {

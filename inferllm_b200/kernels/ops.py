@@ -238,6 +238,38 @@ def attention_decode(qkv, k_cache, v_cache, block_table, token_pos, token_seq, n
     return out
 
 
+GQA_DECODE_CHUNK = 128
+GQA_DECODE_MIN_GROUP = 4        # from this many query heads per KV head on, the MMA kernel is the faster one
+
+
+def attention_decode_gqa_supported(dtype, n_heads, n_kv_heads, head_dim) -> bool:
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and n_heads % n_kv_heads == 0
+            and 2 <= n_heads // n_kv_heads <= 16)
+
+
+def attention_decode_gqa(qkv, k_cache, v_cache, block_table, token_pos, token_seq, n_heads, n_kv_heads,
+                         head_dim, page_size, window, scale, max_len):
+    """bfloat16 attention of single tokens with grouped heads on warp-level MMAs (the query heads
+    of a KV head are the rows of one tile), split over chunks of 128 keys and merged in a fixed
+    order.  Any page size, group sizes 2..16, head size 64 or 128."""
+    _need(qkv, "qkv", torch.bfloat16, 2)
+    _need(k_cache, "k_cache", torch.bfloat16, 4)
+    _need(v_cache, "v_cache", torch.bfloat16, 4)
+    T = qkv.shape[0]
+    n_chunks = max(1, -(-int(max_len) // GQA_DECODE_CHUNK))
+    part_acc = torch.empty((T, n_heads, n_chunks, head_dim), dtype=torch.float32, device=qkv.device)
+    part_ml = torch.empty((T, n_heads, n_chunks, 2), dtype=torch.float32, device=qkv.device)
+    out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    for t0 in range(0, T, 65535):
+        t1 = min(T, t0 + 65535)
+        _check(load().illm_attention_decode_gqa(
+            _ptr(qkv[t0:t1]), qkv.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+            block_table.shape[1], _ptr(token_pos[t0:t1]), _ptr(token_seq[t0:t1]), _ptr(part_acc[t0:t1]),
+            _ptr(part_ml[t0:t1]), _ptr(out[t0:t1]), t1 - t0, n_heads, n_kv_heads, head_dim, page_size,
+            int(window or 0), float(scale), n_chunks, _stream()), "attention_decode_gqa")
+    return out
+
+
 def attention_prefill_supported(dtype, n_heads, n_kv_heads, head_dim) -> bool:
     return dtype == torch.bfloat16 and head_dim in (64, 128) and n_heads % n_kv_heads == 0
 
@@ -284,6 +316,13 @@ def attention_prefill_tc(qkv, k_cache, v_cache, block_table, cu_q, seq_lens, max
 def attention(qkv, kv, ctx, n_heads, n_kv_heads, head_dim, window, scale):
     """Attention of the step's tokens over the cache entry `kv` (a KVView): picks the kernel
     for the dtype, head size and kind of step."""
+    group = n_heads // n_kv_heads if n_kv_heads else 0
+    if ctx.is_decode and (group >= GQA_DECODE_MIN_GROUP or not attention_decode_supported(
+            qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_size)) and attention_decode_gqa_supported(
+            qkv.dtype, n_heads, n_kv_heads, head_dim):
+        return attention_decode_gqa(qkv, kv.k, kv.v, kv.block_table, ctx.token_pos, ctx.token_seq,
+                                    n_heads, n_kv_heads, head_dim, kv.page_size, window, scale,
+                                    ctx.max_seq_len)
     if ctx.is_decode and attention_decode_supported(qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_size):
         # grid and scratch are sized for the longest sequence the cache allows, so that the
         # launch is the same at every step
@@ -418,8 +457,9 @@ GEMM_TC_MAX_TOKENS_AUTO = 16
 
 
 def set_gemm_backend(name: str) -> None:
-    """Which kernel runs the bfloat16 matrix products.  "tc": the package's tcgen05 kernel for
-    every product it can take (K a multiple of 8); "library": cuBLAS through torch.mm; "auto"
+    """Which kernel runs the bfloat16 matrix products.  "tc": the package's tcgen05 kernels for
+    every product they can take (K a multiple of 8): `gemm_tc.cu` up to 128 tokens, the SM-pair
+    kernel `gemm_tc2.cu` above; "library": cuBLAS through torch.mm; "auto"
     (default): the tcgen05 kernel for small decode batches (at most 16 tokens), where its swapped,
     split-K form with weight prefetch across kernel boundaries is faster than the library
     (74.8 against 89.5 us for the four products of a 7B layer at batch 1, 78.1 against 79.4 at
@@ -441,6 +481,8 @@ def linear(x, w, out_dtype=None, defer_reduce=False):
     M, K = x.shape
     if M > 0 and K % 8 == 0 and (_GEMM_BACKEND == "tc" or (
             _GEMM_BACKEND == "auto" and M <= GEMM_TC_MAX_TOKENS_AUTO)):
+        if M > 128 and w.shape[0] >= 256:
+            return gemm_bf16_tc2(x, w, out_dtype or torch.bfloat16)      # prompts: pairs of SMs
         return gemm_bf16_tc(x, w, out_dtype or torch.bfloat16, defer_reduce=defer_reduce)
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)

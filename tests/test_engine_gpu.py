@@ -191,3 +191,21 @@ def test_refusals(model_folders):
     eng.end_sequence(s)
     eng.step([StepItem(t, [1] * 10, [9])])
     eng.check_device_errors()
+
+
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_all_products_on_the_package_kernels(name, model_folders, plain_logits):
+    """gemm="tc": prompts and single tokens both go through the tcgen05 kernels (no library
+    product anywhere in the step) and still match the plain implementation."""
+    from inferllm_b200 import Engine, EngineOptions
+    from inferllm_b200.kernels import ops
+    eng = Engine.from_folder(model_folders[name], EngineOptions(dtype="bfloat16", max_tokens=1024, gemm="tc"))
+    try:
+        for i, n in enumerate(LENGTHS[name]):
+            ids = random_prompt(name, n, 100 + i)
+            assert_close(whole(eng, ids), plain_logits(name, ids), "bfloat16", f"{name} whole n={n}")
+            if n > 40:
+                assert_close(tail_one_by_one(eng, ids), plain_logits(name, ids), "bfloat16", f"{name} tail n={n}")
+        eng.check_device_errors()
+    finally:
+        ops.set_gemm_backend("auto")

@@ -445,6 +445,35 @@ def test_attention_prefill_finds_far_keys_and_respects_the_window_edge():
             assert hit == inside, (window, qrow, target)
 
 
+@pytest.mark.parametrize("nh,nkv,d,page,window", [
+    (8, 2, 128, 64, None), (32, 8, 128, 16, None), (6, 2, 64, 8, None), (10, 2, 128, 64, None),
+    (16, 1, 64, 32, None), (4, 2, 128, 4, 300), (12, 4, 64, 64, 5), (14, 2, 128, 64, None)])
+def test_attention_decode_gqa(nh, nkv, d, page, window):
+    """Grouped heads as rows of an MMA tile: group sizes 2..16 (also ones that are no power of
+    two), any page size, sequences around the chunk borders."""
+    lens = [1, 127, 128, 129, 700, 1024, 3]
+    pc = Paged(lens, nkv, d, page, torch.bfloat16, seed=d + nh)
+    g = torch.Generator().manual_seed(3)
+    T = len(lens)
+    q = torch.randn(T, nh, d, generator=g).bfloat16()
+    qkv = torch.cat([q.reshape(T, nh * d), torch.zeros(T, 2 * nkv * d, dtype=torch.bfloat16)], dim=1)
+    seq = torch.arange(T, dtype=torch.int32)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    scale = 1.0 / math.sqrt(d)
+    assert ops.attention_decode_gqa_supported(torch.bfloat16, nh, nkv, d)
+    for max_len in (1024, 4096):
+        out = ops.attention_decode_gqa(dev(qkv), dev(pc.kc), dev(pc.vc), dev(pc.table), dev(pos), dev(seq),
+                                       nh, nkv, d, page, window, scale, max_len)
+        got = f64(out)
+        assert np.isfinite(got).all()
+        for b in range(T):
+            ref = plain_attention_rows(f64(q[b:b + 1]), f64(pc.k[b]), f64(pc.v[b]), [lens[b] - 1], nh, nkv, scale, window)
+            assert maxrel(got[b:b + 1], ref) <= 2 ** -7, f"sequence of {lens[b]} keys"
+    alone = ops.attention_decode_gqa(dev(qkv[4:5]), dev(pc.kc), dev(pc.vc), dev(pc.table[4:5]), dev(pos[4:5]),
+                                     dev(torch.zeros(1, dtype=torch.int32)), nh, nkv, d, page, window, scale, 4096)
+    assert torch.equal(alone[0].cpu(), out[4].cpu())
+
+
 def test_attention_decode_says_what_it_takes():
     assert not ops.attention_decode_supported(torch.float32, 4, 4, 128, 64)
     assert not ops.attention_decode_supported(torch.bfloat16, 4, 4, 24, 64)
