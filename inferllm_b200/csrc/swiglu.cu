@@ -37,6 +37,43 @@ __global__ void swiglu_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ ou
     store8(out + t * I + c, r);
 }
 
+// The same with the packed projection still in `P` float32 slices of a split matrix product
+// (slice z at slices + z * stride): they are added in ascending order first.
+__global__ void swiglu_partials_kernel(const float* __restrict__ slices, int P, long long stride,
+                                       bf16* __restrict__ out, int I, long long n_vec) {
+    pdl_grid_sync();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_vec) return;
+    const int per_row = I / 8;
+    const long long t = i / per_row;
+    const int c = (int)(i - t * per_row) * 8;
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int z = 0; z < P; z++) {
+        float pa[8], pb[8];
+        load8(slices + (size_t)z * stride + t * 2 * I + c, pa);
+        load8(slices + (size_t)z * stride + t * 2 * I + I + c, pb);
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            a[k] += pa[k];
+            b[k] += pb[k];
+        }
+    }
+    float r[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) r[k] = (a[k] / (1.0f + expf(-a[k]))) * b[k];
+    store8(out + t * I + c, r);
+}
+
+extern "C" int illm_swiglu_partials(const float* slices, int P, long long stride, void* out, int T, int I,
+                                    void* stream) {
+    if (T <= 0 || I <= 0) return 0;
+    if ((I & 7) || P < 1) return ILLM_ERR_BAD_ARG;
+    const long long n_vec = (long long)T * (I / 8);
+    illm_launch(swiglu_partials_kernel, dim3((unsigned)((n_vec + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
+                slices, P, stride, (bf16*)out, I, n_vec);
+    return illm_launch_status();
+}
+
 extern "C" int illm_swiglu(const void* gu, void* out, int act_dtype, int T, int I, void* stream) {
     if (T <= 0 || I <= 0) return 0;
     if (T > 65535 * 32) return ILLM_ERR_BAD_ARG;

@@ -30,6 +30,7 @@ _SIGNATURES = {
     "illm_add_rmsnorm_partials": [P, P, I, LL, P, I, P, I, P, I, I, F, I, P],
     "illm_rope_kv_write_partials": [P, P, I, LL, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, P, P],
     "illm_gemm_bf16_tc2": [P, P, P, I, I, I, I, I, P, P],
+    "illm_swiglu_partials": [P, I, LL, P, I, I, P],
     "illm_gemm_bf16_tc_tune": [I],
     "illm_set_pdl": [I],
     "illm_attention_prefill_tc": [P, I, I, P, P, LL, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P],

@@ -129,7 +129,15 @@ def residual_add(resid, delta):
 
 
 def swiglu(gu):
-    """gu [T, 2I] = [gate | up] -> silu(gate) * up, [T, I]."""
+    """gu [T, 2I] = [gate | up] -> silu(gate) * up, [T, I].  `gu` may be `SplitKPartials`."""
+    if isinstance(gu, SplitKPartials):
+        T, I2 = gu.shape
+        if (I2 // 2) % 8 == 0:
+            out = torch.empty((T, I2 // 2), dtype=torch.bfloat16, device=gu.device)
+            _check(load().illm_swiglu_partials(_ptr(gu.ws), gu.splits, gu.rows * gu.cols, _ptr(out), T, I2 // 2,
+                                               _stream()), "swiglu_partials")
+            return out
+        gu = gu.materialize(torch.bfloat16)
     _need(gu, "gate_up", None, 2)
     T, I2 = gu.shape
     out = torch.empty((T, I2 // 2), dtype=gu.dtype, device=gu.device)

@@ -37,9 +37,9 @@ class GatedMLP(FeedForward):
         self.w_down = tensors["down_proj.weight"].to(dt).contiguous()
 
     def forward(self, h, ctx):
-        gu = ops.linear(h, self.w_gate_up)
+        gu = ops.linear(h, self.w_gate_up, defer_reduce=True)     # the activation kernel adds K slices up
         return ops.linear(ops.swiglu(gu), self.w_down)
 
     def forward_deferred(self, h, ctx):
-        gu = ops.linear(h, self.w_gate_up)
+        gu = ops.linear(h, self.w_gate_up, defer_reduce=True)
         return ops.linear(ops.swiglu(gu), self.w_down, defer_reduce=True)

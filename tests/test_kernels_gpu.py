@@ -214,6 +214,11 @@ def test_unreduced_split_k_slices_feed_norm_and_rope():
     r3 = dev(resid)
     ops.residual_add(r3, part)
     assert maxrel(f64(r3), ref_x) <= 2 ** -8 * np.abs(f64(full)).max()
+    # the gated activation takes slices too
+    wg = (torch.randn(512, 4096, generator=g) * 0.05).bfloat16()
+    pg = ops.gemm_bf16_tc(dev(x), dev(wg), defer_reduce=True, splits=4)
+    fg = f64(pg.materialize(torch.float32))
+    assert maxrel(f64(ops.swiglu(pg)), plain.silu(fg[:, :256]) * fg[:, 256:]) <= 2 ** -7
     # the packed projection of an attention layer: 3 heads + 2 x 1 kv heads of 64 channels
     nh, nkv, d, page = 3, 1, 64, 16
     wq = (torch.randn((nh + 2 * nkv) * d, 4096, generator=g) * 0.05).bfloat16()
