@@ -278,6 +278,47 @@ def attention_decode_gqa(qkv, k_cache, v_cache, block_table, token_pos, token_se
     return out
 
 
+RING_DECODE_MAX_SPLITS = 16
+
+
+def attention_decode_ring_supported(dtype, n_heads, n_kv_heads, head_dim, page_size) -> bool:
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and n_heads % n_kv_heads == 0
+            and n_heads // n_kv_heads <= 16 and page_size % 64 == 0)
+
+
+def attention_decode_ring_splits(T, n_kv_heads, max_len) -> int:
+    """Blocks per (token, kv head): as many as fill the GPU once (two blocks per SM), at most
+    one per 64-key tile of the longest sequence and at most 16."""
+    tiles = max(1, -(-int(max_len) // 64))
+    return max(1, min(2 * N_SMS // max(1, T * n_kv_heads), tiles, RING_DECODE_MAX_SPLITS))
+
+
+def attention_decode_ring(qkv, k_cache, v_cache, block_table, token_pos, token_seq, n_heads, n_kv_heads,
+                          head_dim, page_size, window, scale, max_len, splits=None):
+    """bfloat16 attention of single tokens as a stream: K/V tiles of 64 keys by TMA through a ring
+    of shared-memory stages, the query heads of a KV head as rows of warp-level MMAs, the tiles
+    of a token dealt round-robin to `splits` blocks and merged in a fixed order.  Group sizes
+    1..16, head size 64 or 128, pages of a multiple of 64 positions."""
+    _need(qkv, "qkv", torch.bfloat16, 2)
+    _need(k_cache, "k_cache", torch.bfloat16, 4)
+    _need(v_cache, "v_cache", torch.bfloat16, 4)
+    T = qkv.shape[0]
+    out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    for t0 in range(0, T, 65535):
+        t1 = min(T, t0 + 65535)
+        n = attention_decode_ring_splits(t1 - t0, n_kv_heads, max_len) if splits is None else int(splits)
+        part_acc = part_ml = None
+        if n > 1:
+            part_acc = torch.empty((t1 - t0, n_heads, n, head_dim), dtype=torch.float32, device=qkv.device)
+            part_ml = torch.empty((t1 - t0, n_heads, n, 2), dtype=torch.float32, device=qkv.device)
+        _check(load().illm_attention_decode_ring(
+            _ptr(qkv[t0:t1]), qkv.shape[1], _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table),
+            block_table.shape[1], _ptr(token_pos[t0:t1]), _ptr(token_seq[t0:t1]), _ptr(part_acc), _ptr(part_ml),
+            _ptr(out[t0:t1]), t1 - t0, n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale),
+            n, _ptr(tc_error_word(qkv.device)), _stream()), "attention_decode_ring")
+    return out
+
+
 def attention_prefill_supported(dtype, n_heads, n_kv_heads, head_dim) -> bool:
     return dtype == torch.bfloat16 and head_dim in (64, 128) and n_heads % n_kv_heads == 0
 
@@ -324,6 +365,13 @@ def attention_prefill_tc(qkv, k_cache, v_cache, block_table, cu_q, seq_lens, max
 def attention(qkv, kv, ctx, n_heads, n_kv_heads, head_dim, window, scale):
     """Attention of the step's tokens over the cache entry `kv` (a KVView): picks the kernel
     for the dtype, head size and kind of step."""
+    group = n_heads // n_kv_heads if n_kv_heads else 0
+    # grids and scratch of the decode kernels are sized for the longest sequence the cache allows,
+    # so that the launch is the same at every step
+    if ctx.is_decode and attention_decode_ring_supported(qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_size):
+        return attention_decode_ring(qkv, kv.k, kv.v, kv.block_table, ctx.token_pos, ctx.token_seq,
+                                     n_heads, n_kv_heads, head_dim, kv.page_size, window, scale,
+                                     ctx.max_seq_len)
     group = n_heads // n_kv_heads if n_kv_heads else 0
     if ctx.is_decode and (group >= GQA_DECODE_MIN_GROUP or not attention_decode_supported(
             qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_size)) and attention_decode_gqa_supported(

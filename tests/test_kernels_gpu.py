@@ -479,6 +479,39 @@ def test_attention_decode_gqa(nh, nkv, d, page, window):
     assert torch.equal(alone[0].cpu(), out[4].cpu())
 
 
+@pytest.mark.parametrize("nh,nkv,d,page,window", [
+    (8, 2, 128, 64, None), (32, 8, 128, 128, None), (6, 2, 64, 64, None), (10, 2, 128, 64, None),
+    (16, 1, 64, 192, None), (4, 4, 128, 64, 300), (12, 4, 64, 64, 5), (3, 3, 64, 128, None),
+    (14, 2, 128, 64, 70)])
+def test_attention_decode_ring(nh, nkv, d, page, window):
+    """The streaming kernel: group sizes 1..16, sequences around the tile borders, every number of
+    splits (blocks without keys, blocks with one tile, one block with all of them)."""
+    lens = [1, 63, 64, 65, 700, 1024, 3, 129]
+    pc = Paged(lens, nkv, d, page, torch.bfloat16, seed=d + nh)
+    g = torch.Generator().manual_seed(3)
+    T = len(lens)
+    q = torch.randn(T, nh, d, generator=g).bfloat16()
+    qkv = torch.cat([q.reshape(T, nh * d), torch.zeros(T, 2 * nkv * d, dtype=torch.bfloat16)], dim=1)
+    seq = torch.arange(T, dtype=torch.int32)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    scale = 1.0 / math.sqrt(d)
+    assert ops.attention_decode_ring_supported(torch.bfloat16, nh, nkv, d, page)
+    refs = [plain_attention_rows(f64(q[b:b + 1]), f64(pc.k[b]), f64(pc.v[b]), [lens[b] - 1], nh, nkv, scale, window)
+            for b in range(T)]
+    for splits in (None, 1, 2, 3, 16):
+        out = ops.attention_decode_ring(dev(qkv), dev(pc.kc), dev(pc.vc), dev(pc.table), dev(pos), dev(seq),
+                                        nh, nkv, d, page, window, scale, 4096, splits=splits)
+        got = f64(out)
+        assert np.isfinite(got).all()
+        for b in range(T):
+            assert maxrel(got[b:b + 1], refs[b]) <= 2 ** -7, f"sequence of {lens[b]} keys, {splits} splits"
+    assert int(ops.tc_error_word(torch.device("cuda")).item()) == 0
+    alone = ops.attention_decode_ring(dev(qkv[4:5]), dev(pc.kc), dev(pc.vc), dev(pc.table[4:5]), dev(pos[4:5]),
+                                      dev(torch.zeros(1, dtype=torch.int32)), nh, nkv, d, page, window, scale, 4096,
+                                      splits=16)
+    assert torch.equal(alone[0].cpu(), out[4].cpu())
+
+
 def test_attention_decode_says_what_it_takes():
     assert not ops.attention_decode_supported(torch.float32, 4, 4, 128, 64)
     assert not ops.attention_decode_supported(torch.bfloat16, 4, 4, 24, 64)
