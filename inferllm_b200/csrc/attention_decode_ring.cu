@@ -161,7 +161,8 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
     bool alive = true;
     for (int i = 0; i < n_my && alive; i++) {
         const int s = i % STAGES;
-        alive = mbar_wait(full0 + 8 * s, (i / STAGES) & 1, err);
+        // lanes leave the polling loop one by one: together again before the warp-wide instructions
+        alive = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, (i / STAGES) & 1, err));
         if (!alive) break;
         const int key0 = (tile_lo + split + i * n_splits) * RD_BN + warp * 16;
         if (key0 <= p && key0 + 15 >= lo) {

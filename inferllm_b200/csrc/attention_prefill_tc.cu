@@ -1,22 +1,28 @@
 // Causal attention of whole prompts over the paged cache on the 5th-generation tensor cores.
 //
-// One block owns two tiles of 128 consecutive query tokens of one (sequence, head); each tile has
-// four softmax warps of its own, a thread of which owns one query row, which is also one lane of
-// tensor memory.  Keys and values come in blocks of 64 straight from the cache pages by TMA
-// (128-byte swizzle, double buffered) and serve both tiles.  Per tile and block of keys:
-//   S = Q K^T      tcgen05.mma, M = 128 rows, N = 64 keys, K = head size, accumulator in the
-//                  tile's tensor memory columns [0, 64)
-//   softmax        each thread reads its row of S with tcgen05.ld, scales, masks (causal, window),
-//                  keeps the running maximum and sum in float32, and writes P = exp2(S - max) as
-//                  bfloat16 into shared memory in the swizzled layout the tensor core reads
-//   O_blk = P V    tcgen05.mma with V as an MN-major operand (the cache keeps [position, channel]),
-//                  into columns [64, 64 + head size); the thread adds it to its row of O, which it
-//                  keeps in registers, after scaling O by exp2(old max - new max)
-// so the score matrix never exists in memory and nothing of the running state crosses threads.
-// One more thread issues the MMAs and another the TMA copies; the MMAs of one tile run while the
-// softmax warps of the other tile work, and the scores of a tile's next block are issued right
-// behind its P V.  Formulas as in the reference (src/kern/naive/naive.cpp:606-632, :531-553,
-// :209-240, :664-691), which materialises S in float32 and runs four launches over it
+// One block owns a tile of 128 consecutive query tokens of one (sequence, head); two blocks share
+// an SM.  Four softmax warps: a thread owns one query row, which is also one lane of tensor memory.
+// Keys and values come in blocks of 64 straight from the cache pages by TMA (128-byte swizzle), K
+// through a ring of three stages and V through a ring of two.  Tensor memory of a block, 256
+// columns: two score buffers S0, S1 of 64 columns and the output accumulator O of `head size`.
+// Per block of keys i:
+//   S(i) = Q K^T   tcgen05.mma, M = 128 rows, N = 64 keys, K = head size, into S(i & 1).  It is
+//                  issued one block ahead: the tensor core computes S(i+1) while the softmax warps
+//                  work on S(i).
+//   softmax        a thread reads its row of S(i) with tcgen05.ld (once), masks (causal, window),
+//                  and writes P = exp2(S * scale - m) as bfloat16 pairs back over S(i) with
+//                  tcgen05.st: P never goes through shared memory.  m is the row's reference
+//                  maximum; it follows the true maximum only when that has grown by more than 8
+//                  (a factor of 256, harmless in float32), because moving it means rescaling O in
+//                  tensor memory (tcgen05.ld, multiply, tcgen05.st), and after the first blocks of
+//                  a row that is rare.  The sum of P is kept against the same reference, so the
+//                  result is the exact softmax whatever the reference was.
+//   O += P V       tcgen05.mma with P read from tensor memory (operand A) and V as an MN-major
+//                  shared-memory operand (the cache keeps [position, channel]), accumulating in O.
+// The score matrix never exists in memory, nothing of the running state crosses threads, and O is
+// read once, at the end.  One more thread issues the MMAs and another the TMA copies.
+// Formulas as in the reference (src/kern/naive/naive.cpp:606-632, :531-553, :209-240, :664-691),
+// which materialises S in float32 and runs four launches over it
 // (src/kern/gpu/kernel_gpu.cu:576-609, :504-536, :78-125).
 // Takes head sizes 64 and 128 and page sizes that are multiples of 64; any number of heads and
 // groups; prompts that start at 0 or continue a sequence; an optional window.  Every wait is
@@ -27,11 +33,13 @@
 #include "common.cuh"
 
 #define FT_BM 128            // rows of a query tile = lanes of tensor memory
-#define FT_MAX_TILES 2       // query tiles per block: one's softmax overlaps the other's MMAs
 #define FT_BN 64             // keys per ring block (one page piece)
-#define FT_THREADS(tiles) (32 * (4 * (tiles) + 2))
+#define FT_KSTAGES 3
+#define FT_VSTAGES 2
+#define FT_THREADS 192       // 4 softmax warps, the MMA warp, the TMA warp
 #define FT_WAIT_LIMIT (1 << 22)
 #define FT_ERR_TIMEOUT 5
+#define FT_RESCALE_STEP 8.0f // how far (in powers of two) the maximum may run ahead of the reference
 
 namespace {
 
@@ -78,6 +86,7 @@ __device__ __forceinline__ unsigned long long desc_mnmajor(unsigned addr, unsign
     return (unsigned long long)((addr & 0x3FFFF) >> 4) | ((unsigned long long)(lbo_bytes >> 4) << 16) |
            ((unsigned long long)(1024 >> 4) << 32) | ((unsigned long long)1 << 46) | ((unsigned long long)2 << 61);
 }
+// D[tmem] (+)= A[smem] . B[smem]
 __device__ __forceinline__ void mma_bf16_ss(unsigned tmem_d, unsigned long long da, unsigned long long db,
                                             unsigned idesc, unsigned accumulate) {
     asm volatile(
@@ -86,11 +95,20 @@ __device__ __forceinline__ void mma_bf16_ss(unsigned tmem_d, unsigned long long 
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
+// D[tmem] (+)= A[tmem] . B[smem]: A's row r is lane r, its K elements packed in pairs per column
+__device__ __forceinline__ void mma_bf16_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long db,
+                                            unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void mma_commit(unsigned bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, float* v) {
-    unsigned r[32];
+// 32 consecutive columns of this thread's lane; the values may be used after tmem_wait_ld()
+__device__ __forceinline__ void tmem_ld32_issue(unsigned taddr, unsigned* r) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
@@ -100,39 +118,59 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, float* v) {
           "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
+}
+// Waits for the loads issued so far and pins the registers behind the wait: the compiler sees
+// each of them redefined here, so no use can move above it.
+template <int N> __device__ __forceinline__ void tmem_wait_ld(unsigned* r) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+    for (int i = 0; i < N; i++) asm volatile("" : "+r"(r[i]));
+}
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
 }
 
 }  // namespace
 
-template <int D, int FT_TILES>
-__global__ void __launch_bounds__(FT_THREADS(FT_TILES), FT_TILES == 1 ? 2 : 1)
+template <int D>
+__global__ void __launch_bounds__(FT_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                             int max_pages, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
                             bf16* __restrict__ out, int nh, int nkv, int page_size, int window,
                             float scale_log2e, int* __restrict__ err) {
-    constexpr int FT_MMA_WARP = 4 * FT_TILES, FT_TMA_WARP = 4 * FT_TILES + 1;
+    constexpr int FT_MMA_WARP = 4, FT_TMA_WARP = 5;
     constexpr int NA = D / 64;                            // 64-channel atoms of the head
-    constexpr unsigned Q_TILE = FT_BM * D * 2;            // one query tile: [NA][128 rows][128 B]
+    constexpr unsigned Q_TILE = FT_BM * D * 2;            // the query tile: [NA][128 rows][128 B]
     constexpr unsigned KV_BYTES = FT_BN * D * 2;          // K: [NA][64 keys][128 B]; V: the same shape
-    constexpr unsigned P_TILE = FT_BM * FT_BN * 2;        // [128 rows][128 B] = 64 keys
     constexpr unsigned Q_ATOM = 128 * 128, KV_ATOM = FT_BN * 128;
-    constexpr unsigned TMEM_COLS = 256 * FT_TILES, TILE_COLS = 256, O_COL = FT_BN;   // one-tile blocks share an SM
+    constexpr unsigned TMEM_COLS = 256, S_COLS = FT_BN, O_COL = 2 * FT_BN;
     constexpr unsigned IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(FT_BN >> 3) << 17) | ((unsigned)(FT_BM >> 4) << 24);
     constexpr unsigned IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(D >> 3) << 17) | ((unsigned)(FT_BM >> 4) << 24);
 
     // No static shared memory: the dynamic window then starts on a 1024-byte boundary (the
-    // swizzle's period) and two one-tile blocks fit an SM.  Barriers sit behind the tiles.
+    // swizzle's period) and two blocks fit an SM.  Barriers sit behind the tiles.
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const unsigned base = s_u32(smem_raw);
-    const unsigned q_s = base, k_s = q_s + FT_TILES * Q_TILE, v_s = k_s + 2 * KV_BYTES, p_s = v_s + 2 * KV_BYTES;
-    const unsigned bars0 = p_s + FT_TILES * P_TILE;
-    unsigned* tmem_holder_p = reinterpret_cast<unsigned*>(smem_raw + (bars0 - base) + 11 * 8);
-    const unsigned q_full = bars0, kv_full0 = bars0 + 8, kv_empty0 = bars0 + 24;
-    const unsigned s_full0 = bars0 + 40, p_full0 = bars0 + 56, o_full0 = bars0 + 72;
+    const unsigned q_s = base, k_s = q_s + Q_TILE, v_s = k_s + FT_KSTAGES * KV_BYTES;
+    const unsigned bars0 = v_s + FT_VSTAGES * KV_BYTES;
+    const unsigned q_full = bars0, k_full0 = bars0 + 8, k_empty0 = k_full0 + 8 * FT_KSTAGES;
+    const unsigned v_full0 = k_empty0 + 8 * FT_KSTAGES, v_empty0 = v_full0 + 8 * FT_VSTAGES;
+    const unsigned s_full0 = v_empty0 + 8 * FT_VSTAGES, p_full0 = s_full0 + 16, pv_done = p_full0 + 16;
+    unsigned* tmem_holder_p = reinterpret_cast<unsigned*>(smem_raw + (pv_done + 8 - base));
     if ((base & 1023u) != 0) {          // cannot happen without static shared memory; never run misaligned
         if (threadIdx.x == 0) atomicExch(err, FT_ERR_TIMEOUT + 1);
         return;
@@ -141,13 +179,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         bar_init(q_full, 1);
-        for (int i = 0; i < 2; i++) {
-            bar_init(kv_full0 + 8 * i, 1);
-            bar_init(kv_empty0 + 8 * i, 1);
-            bar_init(s_full0 + 8 * i, 1);
-            bar_init(p_full0 + 8 * i, FT_BM);
-            bar_init(o_full0 + 8 * i, 1);
+        for (int i = 0; i < FT_KSTAGES; i++) {
+            bar_init(k_full0 + 8 * i, 1);
+            bar_init(k_empty0 + 8 * i, 1);
         }
+        for (int i = 0; i < FT_VSTAGES; i++) {
+            bar_init(v_full0 + 8 * i, 1);
+            bar_init(v_empty0 + 8 * i, 1);
+        }
+        bar_init(s_full0, 1);
+        bar_init(s_full0 + 8, 1);
+        bar_init(p_full0, FT_BM);          // one per score buffer: a fast warp may be a block ahead of a slow one
+        bar_init(p_full0 + 8, FT_BM);
+        bar_init(pv_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -162,220 +206,213 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const unsigned tmem = *tmem_holder_p;
     pdl_grid_sync();
 
-    // ---- which rows and keys.  The block owns FT_TILES query tiles of 128 rows; the last blocks of
-    // a prompt see the most keys and start first.
-    const int b = blockIdx.z, h = blockIdx.y, cta_tile = gridDim.x - 1 - blockIdx.x;
+    // ---- which rows and keys.  The last tiles of a prompt see the most keys and start first.
+    const int b = blockIdx.z, h = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
     const int q0 = cu_q[b], qlen = cu_q[b + 1] - q0;
-    const int cta_row0 = cta_tile * FT_TILES * FT_BM;
+    const int row0 = tile * FT_BM;
     const int total = seq_lens[b], past = total - qlen;
     const int hk = h / (nh / nkv);
-    const int cta_rows = (qlen - cta_row0 < FT_TILES * FT_BM) ? qlen - cta_row0 : FT_TILES * FT_BM;   // <= 0: nothing
-    const bool cta_has_rows = cta_rows > 0;
-    const int cta_first_pos = past + cta_row0, cta_last_pos = cta_first_pos + cta_rows - 1;
-    const int lo_key = (window > 0 && cta_first_pos - window + 1 > 0) ? cta_first_pos - window + 1 : 0;
-    const int jb0 = lo_key / FT_BN;                               // first key block of the block's ring
-    const int n_blocks = cta_has_rows ? cta_last_pos / FT_BN - jb0 + 1 : 0;
+    const int rows = (qlen - row0 < FT_BM) ? qlen - row0 : FT_BM;          // <= 0: nothing to do
+    const bool has_rows = rows > 0;
+    const int first_pos = past + row0, last_pos = first_pos + rows - 1;
+    const int lo_key = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
+    const int jb0 = lo_key / FT_BN;                                        // first key block
+    const int n_blocks = has_rows ? last_pos / FT_BN - jb0 + 1 : 0;
     const int* bt = block_table + (size_t)b * max_pages;
-    // per tile: rows, and the range [lo_t, hi_t) of ring blocks it needs (ring block i = key block jb0 + i)
-    int rows_t[FT_TILES], lo_t[FT_TILES], hi_t[FT_TILES];
-#pragma unroll
-    for (int t = 0; t < FT_TILES; t++) {
-        const int r0 = cta_row0 + t * FT_BM;
-        rows_t[t] = (qlen - r0 < FT_BM) ? qlen - r0 : FT_BM;
-        if (rows_t[t] < 0) rows_t[t] = 0;
-        const int fp = past + r0, lp = fp + rows_t[t] - 1;
-        const int lk = (window > 0 && fp - window + 1 > 0) ? fp - window + 1 : 0;
-        lo_t[t] = rows_t[t] > 0 ? lk / FT_BN - jb0 : 0;
-        hi_t[t] = rows_t[t] > 0 ? lp / FT_BN - jb0 + 1 : 0;
-    }
 
     if (warp == FT_TMA_WARP) {
-        // ---- TMA producer
-        if (lane == 0 && cta_has_rows) {
-            bar_expect_tx(q_full, FT_TILES * Q_TILE);
-            for (int t = 0; t < FT_TILES; t++)
-                for (int a = 0; a < NA; a++)
-                    tma_2d(q_s + t * Q_TILE + a * Q_ATOM, &map_q, h * D + 64 * a, q0 + cta_row0 + t * FT_BM, q_full);
-            bool alive = true;
-            for (int i = 0; i < n_blocks && alive; i++) {
-                const int buf = i & 1;
-                if (i >= 2) alive = bar_wait(kv_empty0 + 8 * buf, ((i >> 1) - 1) & 1, err);
-                if (!alive) break;
+        // ---- TMA producer.  K(i) may be refilled once S(i-3) has been computed, V(i) once P V of
+        // block i-2 has; the loop asks in the order in which those come true.
+        if (lane == 0 && has_rows) {
+            bar_expect_tx(q_full, Q_TILE);
+            for (int a = 0; a < NA; a++) tma_2d(q_s + a * Q_ATOM, &map_q, h * D + 64 * a, q0 + row0, q_full);
+            auto kv_row = [&](int i) {
                 const int key0 = (jb0 + i) * FT_BN;
-                const int page = bt[key0 / page_size];
-                const int row = (page * nkv + hk) * page_size + (key0 % page_size);
-                bar_expect_tx(kv_full0 + 8 * buf, 2 * KV_BYTES);
-                for (int a = 0; a < NA; a++) {
-                    tma_2d(k_s + buf * KV_BYTES + a * KV_ATOM, &map_k, 64 * a, row, kv_full0 + 8 * buf);
-                    tma_2d(v_s + buf * KV_BYTES + a * KV_ATOM, &map_v, 64 * a, row, kv_full0 + 8 * buf);
-                }
+                return (bt[key0 / page_size] * nkv + hk) * page_size + (key0 % page_size);
+            };
+            bool alive = true;
+            auto load_k = [&](int i) {
+                const int st = i % FT_KSTAGES;
+                if (i >= FT_KSTAGES && !bar_wait(k_empty0 + 8 * st, ((i / FT_KSTAGES) - 1) & 1, err)) return false;
+                const int row = kv_row(i);
+                bar_expect_tx(k_full0 + 8 * st, KV_BYTES);
+                for (int a = 0; a < NA; a++) tma_2d(k_s + st * KV_BYTES + a * KV_ATOM, &map_k, 64 * a, row, k_full0 + 8 * st);
+                return true;
+            };
+            auto load_v = [&](int i) {
+                const int st = i % FT_VSTAGES;
+                if (i >= FT_VSTAGES && !bar_wait(v_empty0 + 8 * st, ((i / FT_VSTAGES) - 1) & 1, err)) return false;
+                const int row = kv_row(i);
+                bar_expect_tx(v_full0 + 8 * st, KV_BYTES);
+                for (int a = 0; a < NA; a++) tma_2d(v_s + st * KV_BYTES + a * KV_ATOM, &map_v, 64 * a, row, v_full0 + 8 * st);
+                return true;
+            };
+            for (int i = 0; i < FT_KSTAGES && i < n_blocks && alive; i++) alive = load_k(i);
+            for (int i = 0; i < FT_VSTAGES && i < n_blocks && alive; i++) alive = load_v(i);
+            for (int i = 0; alive && (i + FT_KSTAGES < n_blocks || i + FT_VSTAGES < n_blocks); i++) {
+                if (i + FT_KSTAGES < n_blocks) alive = load_k(i + FT_KSTAGES);
+                if (alive && i + FT_VSTAGES < n_blocks) alive = load_v(i + FT_VSTAGES);
             }
         }
     } else if (warp == FT_MMA_WARP) {
-        // ---- MMA issuer: for every ring block, P V of each tile as soon as its P is there, and the
-        // scores of the next block for that tile right behind it
-        if (lane == 0 && cta_has_rows) {
+        // ---- MMA issuer: S one block ahead of the softmax, P V as soon as P is there
+        if (lane == 0 && has_rows) {
             bool alive = bar_wait(q_full, 0, err);
-            int n_s[FT_TILES], n_p[FT_TILES];     // how many S / P V products each tile has been issued
-#pragma unroll
-            for (int t = 0; t < FT_TILES; t++) n_s[t] = n_p[t] = 0;
-            auto issue_s = [&](int t, int i) {
-                const int buf = i & 1;
-                if (!bar_wait(kv_full0 + 8 * buf, (i >> 1) & 1, err)) return false;
+            auto issue_s = [&](int i) {
+                const int st = i % FT_KSTAGES;
+                if (!bar_wait(k_full0 + 8 * st, (i / FT_KSTAGES) & 1, err)) return false;
                 fence_after();
 #pragma unroll
                 for (int kk = 0; kk < D / 16; kk++) {
-                    const unsigned qo = t * Q_TILE + (kk >> 2) * Q_ATOM + (kk & 3) * 32;
-                    const unsigned ko = buf * KV_BYTES + (kk >> 2) * KV_ATOM + (kk & 3) * 32;
-                    mma_bf16_ss(tmem + t * TILE_COLS, desc_kmajor(q_s + qo), desc_kmajor(k_s + ko), IDESC_S, kk > 0);
+                    const unsigned qo = (kk >> 2) * Q_ATOM + (kk & 3) * 32;
+                    const unsigned ko = st * KV_BYTES + (kk >> 2) * KV_ATOM + (kk & 3) * 32;
+                    mma_bf16_ss(tmem + (i & 1) * S_COLS, desc_kmajor(q_s + qo), desc_kmajor(k_s + ko), IDESC_S, kk > 0);
                 }
-                mma_commit(s_full0 + 8 * t);
-                n_s[t]++;
+                mma_commit(s_full0 + 8 * (i & 1));     // the scores are there
+                mma_commit(k_empty0 + 8 * st);         // and the K stage has been read
                 return true;
             };
-#pragma unroll
-            for (int t = 0; t < FT_TILES; t++)
-                if (alive && lo_t[t] == 0 && hi_t[t] > 0) alive = issue_s(t, 0);
+            if (alive && n_blocks > 0) alive = issue_s(0);
             for (int i = 0; i < n_blocks && alive; i++) {
-                const int buf = i & 1;
+                // S(i+1) overwrites the buffer that held P(i-1); P V of block i-1 was issued before
+                // and the tensor core runs its instructions in order
+                if (i + 1 < n_blocks) alive = issue_s(i + 1);
+                if (!alive) break;
+                alive = bar_wait(p_full0 + 8 * (i & 1), (i >> 1) & 1, err);
+                if (!alive) break;
+                const int st = i % FT_VSTAGES;
+                alive = bar_wait(v_full0 + 8 * st, (i / FT_VSTAGES) & 1, err);
+                if (!alive) break;
+                fence_after();
 #pragma unroll
-                for (int t = 0; t < FT_TILES; t++) {
-                    if (!alive) break;
-                    if (i >= lo_t[t] && i < hi_t[t]) {
-                        alive = bar_wait(p_full0 + 8 * t, n_p[t] & 1, err);
-                        if (!alive) break;
-                        fence_after();
-#pragma unroll
-                        for (int ks = 0; ks < FT_BN / 16; ks++)
-                            mma_bf16_ss(tmem + t * TILE_COLS + O_COL, desc_kmajor(p_s + t * P_TILE + ks * 32),
-                                        desc_mnmajor(v_s + buf * KV_BYTES + ks * 16 * 128, KV_ATOM), IDESC_O, ks > 0);
-                        mma_commit(o_full0 + 8 * t);
-                        n_p[t]++;
-                    }
-                    // after the last tile's products: everything that reads this ring block has been
-                    // issued, so its completion frees the block for the loader
-                    if (t == FT_TILES - 1) mma_commit(kv_empty0 + 8 * buf);
-                    if (i + 1 >= lo_t[t] && i + 1 < hi_t[t]) alive = issue_s(t, i + 1);
-                }
+                for (int ks = 0; ks < FT_BN / 16; ks++)
+                    mma_bf16_ts(tmem + O_COL, tmem + (i & 1) * S_COLS + ks * 8,
+                                desc_mnmajor(v_s + st * KV_BYTES + ks * 16 * 128, KV_ATOM), IDESC_O, (i > 0 || ks > 0) ? 1u : 0u);
+                mma_commit(v_empty0 + 8 * st);
+                mma_commit(pv_done);
             }
         }
-    } else if (warp < 4 * FT_TILES) {
-        // ---- softmax and accumulation: thread = query row = lane of tensor memory
-        const int t = warp >> 2;                          // which tile this warp group works on
-        const int r = threadIdx.x & 127;                  // row inside the tile
-        const unsigned lane_addr = ((unsigned)((warp & 3) * 32) << 16) + t * TILE_COLS;
-        const int first_pos = cta_first_pos + t * FT_BM;
-        const int last_pos = first_pos + rows_t[t] - 1;
-        const int pos = (r < rows_t[t]) ? first_pos + r : last_pos;
-        float m_run = -INFINITY, l_run = 0.f;
-        float o_reg[D];
-#pragma unroll
-        for (int c = 0; c < D; c++) o_reg[c] = 0.f;
-        bool alive = true;
-        int n = 0;                                        // blocks this tile has processed
-        for (int i = lo_t[t]; i < hi_t[t] && alive; i++, n++) {
+    } else {
+        // ---- softmax: thread = query row = lane of tensor memory
+        const int r = threadIdx.x & 127;
+        const unsigned lane_addr = tmem + ((unsigned)(warp * 32) << 16);
+        const int pos = (r < rows) ? first_pos + r : last_pos;
+        float m_ref = -INFINITY, l_run = 0.f;
+        bool alive = has_rows;
+        for (int i = 0; i < n_blocks && alive; i++) {
             const int key0 = (jb0 + i) * FT_BN;
-            const int buf = i & 1;
-            alive = bar_wait(s_full0 + 8 * t, n & 1, err);
+            // the lanes leave the polling loop one by one: they are brought together again (and agree on
+            // the outcome) before the warp-wide tensor-memory instructions
+            alive = __all_sync(0xffffffffu, bar_wait(s_full0 + 8 * (i & 1), (i >> 1) & 1, err));
             if (!alive) break;
             fence_after();
+            const unsigned s_addr = lane_addr + (i & 1) * S_COLS;
+            unsigned sr[FT_BN];
+            tmem_ld32_issue(s_addr, sr);
+            tmem_ld32_issue(s_addr + 32, sr + 32);
+            tmem_wait_ld<FT_BN>(sr);
             const bool need_mask = (key0 + FT_BN - 1 > first_pos) || (window > 0);
-            // pass 1: the row's maximum over this block (the scale is positive: it is applied to
-            // the maximum, not to every score)
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < FT_BN; c0 += 32) {
-                float v[32];
-                tmem_ld32(tmem + lane_addr + c0, v);
-                if (need_mask) {
+            if (need_mask) {
 #pragma unroll
-                    for (int c = 0; c < 32; c++) {
-                        const int key = key0 + c0 + c;
-                        const bool hide = key > pos || (window > 0 && key < pos - window + 1);
-                        mx = fmaxf(mx, hide ? -INFINITY : v[c]);
-                    }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 32; c++) mx = fmaxf(mx, v[c]);
+                for (int c = 0; c < FT_BN; c++) {
+                    const int key = key0 + c;
+                    const bool hide = key > pos || (window > 0 && key < pos - window + 1);
+                    if (hide) sr[c] = 0xff800000u;      // -inf
                 }
             }
-            const float m_new = fmaxf(m_run, mx * scale_log2e);
-            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_use);
-            m_run = m_new;
-            // pass 2: P = exp2(S * scale - max) -> shared memory (row r of the K-major, swizzled P tile)
-            float ps[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-            for (int c0 = 0; c0 < FT_BN; c0 += 32) {
-                float v[32];
-                tmem_ld32(tmem + lane_addr + c0, v);
-                if (need_mask) {
+            // the row's maximum over this block (the scale is positive: it is applied to the maximum)
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-                    for (int c = 0; c < 32; c++) {
-                        const int key = key0 + c0 + c;
-                        const bool hide = key > pos || (window > 0 && key < pos - window + 1);
-                        v[c] = hide ? 0.f : fast_exp2(fmaf(v[c], scale_log2e, -m_use));
-                    }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 32; c++) v[c] = fast_exp2(fmaf(v[c], scale_log2e, -m_use));
-                }
-#pragma unroll
-                for (int c = 0; c < 32; c++) ps[c & 3] += v[c];
-                const unsigned row_addr = p_s + t * P_TILE + r * 128;
-#pragma unroll
-                for (int q4 = 0; q4 < 4; q4++) {     // four 16-byte chunks of 8 keys
-                    const int chunk = (c0 >> 3) + q4;
-                    uint4 u;
-                    __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&u);
-#pragma unroll
-                    for (int e = 0; e < 4; e++) hp[e] = __floats2bfloat162_rn(v[q4 * 8 + 2 * e], v[q4 * 8 + 2 * e + 1]);
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(row_addr + ((chunk ^ (r & 7)) << 4)),
-                                 "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w) : "memory");
-                }
+            for (int c = 0; c < FT_BN; c += 4) {
+                mx0 = fmaxf(mx0, __uint_as_float(sr[c]));
+                mx1 = fmaxf(mx1, __uint_as_float(sr[c + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(sr[c + 2]));
+                mx3 = fmaxf(mx3, __uint_as_float(sr[c + 3]));
             }
-            const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
-            l_run = l_run * corr + psum;
-            // the block's last ring block may hold positions beyond the sequence: whatever the cache
-            // has there must not reach the product (0 x NaN), so those rows of V are cleared (by
-            // every tile that uses the block: the writes are the same)
-            if (key0 + FT_BN - 1 > cta_last_pos) {
-                alive = bar_wait(kv_full0 + 8 * buf, (i >> 1) & 1, err);
-                const int key = key0 + r;
-                if (r < FT_BN && key > cta_last_pos) {
+            const float m_new = fmaxf(m_ref, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2e);
+            // move the reference only when the maximum has run away from it (always at the first
+            // finite maximum); the decision is the warp's, because the rescaling of O is
+            const bool grown = m_new > m_ref + FT_RESCALE_STEP;      // true for m_ref = -inf, m_new finite
+            bool pv_seen = false;
+            if (__any_sync(0xffffffffu, grown)) {
+                if (i > 0) {
+                    pv_seen = true;
+                    const float corr = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);   // m_new finite or both -inf
+                    const float corr_use = (m_new == -INFINITY) ? 1.f : corr;
+                    alive = __all_sync(0xffffffffu, bar_wait(pv_done, (i - 1) & 1, err));   // O holds blocks 0 .. i-1
+                    if (!alive) break;
+                    fence_after();
+#pragma unroll 1
+                    for (int c0 = 0; c0 < D; c0 += 32) {
+                        unsigned orr[32];
+                        tmem_ld32_issue(lane_addr + O_COL + c0, orr);
+                        tmem_wait_ld<32>(orr);
+#pragma unroll
+                        for (int c = 0; c < 32; c++) orr[c] = __float_as_uint(__uint_as_float(orr[c]) * corr_use);
+                        tmem_st32(lane_addr + O_COL + c0, orr);
+                    }
+                    tmem_wait_st();
+                    l_run *= corr_use;
+                }
+                m_ref = m_new;
+            }
+            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            // P = exp2(S * scale - reference) as bfloat16 pairs over the first 32 columns of S(i)
+            unsigned pr[FT_BN / 2];
+            float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+            for (int c = 0; c < FT_BN; c += 2) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c]), scale_log2e, -m_use));       // exp2(-inf) = 0
+                const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c + 1]), scale_log2e, -m_use));
+                ps0 += p0;
+                ps1 += p1;
+                pr[c >> 1] = pack_bf16(p0, p1);
+            }
+            l_run += ps0 + ps1;
+            tmem_st32(s_addr, pr);
+            tmem_wait_st();
+            // the prompt's last block may hold positions beyond the sequence: whatever the cache
+            // has there must not reach the product (0 x NaN), so those rows of V are cleared
+            if (key0 + FT_BN - 1 > last_pos) {
+                const int st = i % FT_VSTAGES;
+                alive = __all_sync(0xffffffffu, bar_wait(v_full0 + 8 * st, (i / FT_VSTAGES) & 1, err));
+                if (r < FT_BN && key0 + r > last_pos) {
 #pragma unroll
                     for (int a = 0; a < NA; a++) {
-                        const unsigned row_addr = v_s + buf * KV_BYTES + a * KV_ATOM + r * 128;
+                        const unsigned row_addr = v_s + st * KV_BYTES + a * KV_ATOM + r * 128;
 #pragma unroll
                         for (int q8 = 0; q8 < 8; q8++)
                             asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(row_addr + q8 * 16), "r"(0u) : "memory");
                     }
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // Every phase of pv_done is observed, in order, before this thread lets the next one
+            // begin: a wait on a phase's parity is only meaningful while the barrier is at most one
+            // phase away.  P V of the previous block ended long ago by now; this does not stall.
+            if (i > 0 && !pv_seen) alive = __all_sync(0xffffffffu, bar_wait(pv_done, (i - 1) & 1, err));
             fence_before();
-            bar_arrive(p_full0 + 8 * t);
-            // O = O * corr + P V
-            alive = alive && bar_wait(o_full0 + 8 * t, n & 1, err);
-            if (!alive) break;
-            fence_after();
-#pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
-                float v[32];
-                tmem_ld32(tmem + lane_addr + O_COL + c0, v);
-#pragma unroll
-                for (int c = 0; c < 32; c++) o_reg[c0 + c] = fmaf(o_reg[c0 + c], corr, v[c]);
-            }
+            bar_arrive(p_full0 + 8 * (i & 1));
         }
-        if (alive && r < rows_t[t]) {
+        if (alive && n_blocks > 0) alive = __all_sync(0xffffffffu, bar_wait(pv_done, (n_blocks - 1) & 1, err));
+        if (alive && n_blocks > 0) {
+            fence_after();
             const float inv = 1.0f / l_run;
-            bf16* dst = out + ((size_t)(q0 + cta_row0 + t * FT_BM + r) * nh + h) * D;
+            bf16* dst = out + ((size_t)(q0 + row0 + r) * nh + h) * D;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                unsigned orr[32];
+                tmem_ld32_issue(lane_addr + O_COL + c0, orr);
+                tmem_wait_ld<32>(orr);
+                if (r < rows) {
 #pragma unroll
-            for (int c = 0; c < D; c += 8) {
-                float f[8];
+                    for (int c = 0; c < 32; c += 8) {
+                        float f[8];
 #pragma unroll
-                for (int e = 0; e < 8; e++) f[e] = o_reg[c + e] * inv;
-                store8(dst + c, f);
+                        for (int e = 0; e < 8; e++) f[e] = __uint_as_float(orr[c + e]) * inv;
+                        store8(dst + c0 + c, f);
+                    }
+                }
             }
         }
     }
@@ -419,7 +456,7 @@ static int ft_make_map(CUtensorMap* map, const void* ptr, long long rows, long l
     return r == CUDA_SUCCESS ? 0 : ILLM_ERR_BAD_ARG;
 }
 
-template <int D, int TILES>
+template <int D>
 static int ft_launch(const void* q, int q_stride, int T, const void* kc, const void* vc, long long n_pages,
                      const int* block_table, int max_pages, const int* cu_q, const int* seq_lens, void* out, int B,
                      int max_q, int nh, int nkv, int page_size, int window, float scale, int* err, cudaStream_t s) {
@@ -429,29 +466,15 @@ static int ft_launch(const void* q, int q_stride, int T, const void* kc, const v
     const long long kv_rows = n_pages * nkv * page_size;
     if ((rc = ft_make_map(&mk, kc, kv_rows, D, D, FT_BN)) != 0) return rc;
     if ((rc = ft_make_map(&mv, vc, kv_rows, D, D, FT_BN)) != 0) return rc;
-    const size_t smem = (size_t)TILES * FT_BM * D * 2 + 4 * (size_t)FT_BN * D * 2 +
-                        (size_t)TILES * FT_BM * FT_BN * 2 + 128;   // + barriers and the tensor-memory address
-    auto kern = attention_prefill_tc_kernel<D, TILES>;
+    const size_t smem = (size_t)FT_BM * D * 2 + (size_t)(FT_KSTAGES + FT_VSTAGES) * FT_BN * D * 2 +
+                        256;   // + barriers and the tensor-memory address
+    auto kern = attention_prefill_tc_kernel<D>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    dim3 grid((max_q + TILES * FT_BM - 1) / (TILES * FT_BM), nh, B);
-    illm_launch(kern, grid, dim3(FT_THREADS(TILES)), smem, s, mq, mk, mv, block_table, max_pages, cu_q, seq_lens,
+    dim3 grid((max_q + FT_BM - 1) / FT_BM, nh, B);
+    illm_launch(kern, grid, dim3(FT_THREADS), smem, s, mq, mk, mv, block_table, max_pages, cu_q, seq_lens,
                 (bf16*)out, nh, nkv, page_size, window, scale * 1.4426950408889634f, err);
     return illm_launch_status();
-}
-
-// Two query tiles per block when that still gives every SM several blocks; one tile otherwise
-// (short prompts: more, smaller blocks balance the causal triangle better).
-template <int D>
-static int ft_pick(const void* q, int q_stride, int T, const void* kc, const void* vc, long long n_pages,
-                   const int* block_table, int max_pages, const int* cu_q, const int* seq_lens, void* out, int B,
-                   int max_q, int nh, int nkv, int page_size, int window, float scale, int* err, cudaStream_t s) {
-    const long long blocks2 = (long long)((max_q + 2 * FT_BM - 1) / (2 * FT_BM)) * nh * B;
-    if (blocks2 >= 4 * 148)
-        return ft_launch<D, 2>(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q,
-                               nh, nkv, page_size, window, scale, err, s);
-    return ft_launch<D, 1>(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q,
-                           nh, nkv, page_size, window, scale, err, s);
 }
 
 // q: the packed projection [T, q_stride] whose first nh*d columns are the query heads;
@@ -467,10 +490,10 @@ extern "C" int illm_attention_prefill_tc(const void* q, int q_stride, int T, con
         return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     if (d == 128)
-        return ft_pick<128>(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q,
+        return ft_launch<128>(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q,
                               nh, nkv, page_size, window, scale, err, s);
     if (d == 64)
-        return ft_pick<64>(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q,
+        return ft_launch<64>(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q,
                              nh, nkv, page_size, window, scale, err, s);
     return ILLM_ERR_BAD_ARG;
 }

@@ -126,7 +126,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // epilogue: warp w may touch the 32 lanes of tensor memory of its quadrant w % 4
         const int quad = warp & 3;
         asm volatile("griddepcontrol.wait;" ::: "memory");   // before any store: the output may alias
-        const bool ok = mbar_wait(done_bar, 0, err);
+        // lanes leave the polling loop one by one: together again before the warp-wide tcgen05.ld
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(done_bar, 0, err));
         tc_fence_after();
         const int ra = ra0 + quad * 32 + lane;
         TOut* Cz = C + (size_t)blockIdx.z * split_stride;

@@ -174,7 +174,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int t = pair; t < n_tiles && alive; t += n_pairs, ti++) {
             const int buf = ti & 1;
             const int ra = (t % n_m) * 256 + (int)rank * 128 + quad * 32 + lane, rb0 = (t / n_m) * T2_BN;
-            alive = mbar_wait(acc_full0 + 8 * buf, (ti >> 1) & 1, err);
+            // lanes leave the polling loop one by one: together again before the warp-wide tcgen05.ld
+            alive = __all_sync(0xffffffffu, mbar_wait(acc_full0 + 8 * buf, (ti >> 1) & 1, err));
             if (!alive) break;
             tc_fence_after();
             const unsigned tbase = tmem + ((unsigned)(quad * 32) << 16) + (unsigned)(buf * T2_BN);

@@ -406,6 +406,15 @@ def test_attention_prefill_tc(nh, nkv, d, page, window):
         ref = plain_attention_rows(f64(q[rows]), f64(pc.k[b]), f64(pc.v[b]), list(range(starts[b], lens[b])),
                                    nh, nkv, scale, window)
         assert maxrel(got[rows], ref) <= 2 ** -7, f"sequence {b}"
+    # the same inputs evicted from the L2 cache: loads that take long must change nothing (a wait
+    # that passes too early only shows when the data is late)
+    args = (dev(qkv), dev(pc.kc), dev(pc.vc), dev(pc.table), dev(cu), dev(torch.tensor(lens, dtype=torch.int32)))
+    for _ in range(2):
+        flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
+        flush += 1
+        torch.cuda.synchronize()
+        cold = ops.attention_prefill_tc(*args, max(q_lens), nh, nkv, d, page, window, scale)
+        assert torch.equal(cold.cpu(), out.cpu())
 
 
 def test_attention_prefill_tc_finds_far_keys_and_respects_the_window_edge():
@@ -510,6 +519,13 @@ def test_attention_decode_ring(nh, nkv, d, page, window):
                                       dev(torch.zeros(1, dtype=torch.int32)), nh, nkv, d, page, window, scale, 4096,
                                       splits=16)
     assert torch.equal(alone[0].cpu(), out[4].cpu())
+    # inputs evicted from the L2 cache: late data must change nothing
+    args = (dev(qkv), dev(pc.kc), dev(pc.vc), dev(pc.table), dev(pos), dev(seq))
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
+    flush += 1
+    torch.cuda.synchronize()
+    cold = ops.attention_decode_ring(*args, nh, nkv, d, page, window, scale, 4096, splits=16)
+    assert torch.equal(cold.cpu(), out.cpu())
 
 
 def test_attention_decode_says_what_it_takes():
