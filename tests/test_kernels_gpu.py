@@ -242,6 +242,20 @@ def test_unreduced_split_k_slices_feed_norm_and_rope():
         pg = int(table[0, p_ // page])
         assert maxrel(f64(kc)[pg, :, p_ % page], want[i, nh:]) <= 2 ** -8
         assert maxrel(f64(vc)[pg, :, p_ % page], src[i, nh + nkv:]) <= 2 ** -8
+    # a rotation over the first 32 of the 64 channels only: the other channels of Q and K are the sums
+    # of the slices, unrotated
+    rot = 32
+    rope32 = build_part("position", PartSpec("rope_half", dict(head_dim=d, rot_dim=rot, theta=1e4, max_positions=64)),
+                        Runtime(torch.device("cuda"), torch.bfloat16))
+    rope32.prepare()
+    kc.zero_()
+    vc.zero_()
+    out = ops.rope_kv_write(part, rope32.table, rot, pos, seq, table, kc, vc, nh, nkv, d, page, True, err_word())
+    want = plain.rope_rotate_half(src[:, :nh + nkv], pos.cpu().numpy(), 1e4, rot_dim=rot)
+    assert maxrel(f64(out).reshape(M, nh + 2 * nkv, d)[:, :nh], want[:, :nh]) <= 2 ** -8
+    for i, p_ in enumerate(pos.tolist()):
+        pg = int(table[0, p_ // page])
+        assert maxrel(f64(kc)[pg, :, p_ % page], want[i, nh:]) <= 2 ** -8
 
 
 # ---- rope + cache write, attention: a hand-made paged cache
