@@ -96,6 +96,7 @@ __device__ __forceinline__ void pdl_grid_sync() {
 }
 
 inline int g_illm_pdl = 1;   // illm_set_pdl() switches the launch attribute off (e.g. for profilers)
+inline long long g_illm_launches = 0;   // kernels launched by this library (illm_launch_count())
 
 template <typename... KArgs, typename... Args>
 static inline void illm_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
@@ -110,6 +111,7 @@ static inline void illm_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, si
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_illm_pdl ? 1 : 0;
+    g_illm_launches++;
     cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 

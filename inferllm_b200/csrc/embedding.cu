@@ -49,3 +49,7 @@ extern "C" int illm_set_pdl(int on) {
     g_illm_pdl = on ? 1 : 0;
     return 0;
 }
+
+// How many kernels the library has launched in this process (a launch into a stream capture counts
+// once; replays of the captured graph are the caller's to count).
+extern "C" long long illm_launch_count() { return g_illm_launches; }

@@ -34,6 +34,7 @@ _SIGNATURES = {
     "illm_swiglu_partials": [P, I, LL, P, I, I, P],
     "illm_gemm_bf16_tc_tune": [I],
     "illm_set_pdl": [I],
+    "illm_launch_count": [],
     "illm_attention_prefill_tc": [P, I, I, P, P, LL, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P],
     "illm_gemm_f32_nt": [P, P, P, I, I, I, I, I, I, P],
     "illm_argmax": [P, I, I, I, P, P],
@@ -64,6 +65,6 @@ def load():
             raise KernelLibraryError(f"{path} lacks the entry point {name}: rebuild with "
                                      "`python -m inferllm_b200.kernels.build --force`") from None
         fn.argtypes = args
-        fn.restype = c_int
+        fn.restype = c_longlong if name == "illm_launch_count" else c_int
     _lib = lib
     return lib

@@ -25,23 +25,23 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-_launches = 0
+_replayed = 0
 
 
 def launch_count() -> int:
-    """How many kernels of this package have been launched (library products not counted)."""
-    return _launches
+    """How many kernels of this package have been launched: the library counts every kernel it
+    launches (a launch into a stream capture once), replays of captured graphs are added by
+    `count_launches`.  Library products (cuBLAS) are not counted."""
+    return int(load().illm_launch_count()) + _replayed
 
 
 def count_launches(n: int) -> None:
     """Account for kernels launched by replaying a captured graph."""
-    global _launches
-    _launches += n
+    global _replayed
+    _replayed += n
 
 
 def _check(code, what):
-    global _launches
-    _launches += 1
     if code != 0:
         if code == 10001:
             raise KernelError(f"{what}: the kernel refused its arguments")
