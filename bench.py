@@ -127,6 +127,49 @@ def prefill_flops(cfg, n_layers, T, fig):
     return linear + attn
 
 
+SCENARIOS = {"8b": "16:64:2048:256", "13b": "32:128:1024:256", "7b": "8:512:512:256"}
+
+
+def run_scenario(args, cfg, cfgd, model_name, L, fig, pk, pk_src):
+    """An unequal batch through `Model.generate`: one prompt step, then one token per sequence and
+    step, host token ids in and out.  Prints one JSON line with prompt and decode tokens per second
+    and the fraction of the memory rate the decode steps reach (weights once per step plus the live
+    cache at the mean context)."""
+    import torch
+
+    from inferllm_b200 import Model, ModelConfig
+    from inferllm_b200.kernels import ops
+
+    spec = SCENARIOS[args.model] if args.scenario == "config" else args.scenario
+    B, lo, hi, new = (int(x) for x in spec.split(":"))
+    g = torch.Generator().manual_seed(0)
+    lens = torch.randint(lo, hi + 1, (B,), generator=g).tolist()
+    prompts = [torch.randint(0, cfgd["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    ctx = max(lens) + new + 1
+    max_tokens = sum(-(-(n + new + 1) // 64) * 64 for n in lens) + 64
+    model = Model(ModelConfig(compt_type="bfloat16", nr_ctx=ctx, max_tokens=max_tokens, max_batch=B))
+    model.load_random(cfg, seed=0)
+    ops.set_gemm_backend(args.gemm)
+    model.init(top_k=0, top_p=1.0, temp=0.0, repeat_penalty=1.0, repeat_last_n=0, seed=0, end_token=-1)
+    model.generate([p[:64] for p in prompts], max_new_tokens=4, stop_ids=[])       # compile, capture
+    with ClockSampler() as cs:
+        res = model.generate(prompts, max_new_tokens=new, stop_ids=[])
+    steps = res.step_s[max(3, args.warmup):]
+    dec_ms = sum(steps) / len(steps) * 1e3
+    mean_ctx = sum(lens) / B + new - len(steps) / 2
+    step_bytes = fig["weight_bytes"] + B * mean_ctx * fig["kv_bytes_per_token"]
+    pf_flops = sum(prefill_flops(cfgd, L, n, fig) for n in lens)
+    print(json.dumps({
+        "scenario": spec, "model": model_name, "layers": L, "batch": B, "prompt_lengths": [min(lens), max(lens)],
+        "prompt_tokens": sum(lens), "new_tokens_each": new,
+        "prefill": {"tokens_per_s": round(res.prefill_tokens / res.prefill_s, 1), "ms": round(res.prefill_s * 1e3, 2),
+                    "frac": round(pf_flops / res.prefill_s / (pk["bf16_tflops"] * 1e12), 4)},
+        "decode": {"tokens_per_s": round(B / dec_ms * 1e3, 1), "ms_per_step": round(dec_ms, 4),
+                   "steps_timed": len(steps), "hbm_frac": round(step_bytes / (dec_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)},
+        "peaks": pk_src, "clocks": cs.summary(), "gpu_launches": ops.launch_count()}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -142,6 +185,10 @@ def main():
     ap.add_argument("--gemm", default="auto", choices=["auto", "tc", "library"])
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels without programmatic dependent launch")
     ap.add_argument("--context", type=int, default=CONTEXT, help="position at which the timed decode steps end")
+    ap.add_argument("--scenario", metavar="B:MIN:MAX:NEW", help="beside the contract: B prompts of random ids with "
+                    "lengths uniform in [MIN, MAX] (seeded) prefilled in one step of unequal lengths, then NEW tokens "
+                    "each, through the Python entry point; 'config' = the workload BASELINE.json names for --model "
+                    "(8b: 16:64:2048:256, 13b: 32:128:1024:256 of its 3072+ steps)")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -169,6 +216,9 @@ def main():
     fig = model_figures(cfgd, L)
     pk, pk_src = peaks()
     B = args.batch
+
+    if args.scenario:
+        return run_scenario(args, cfg, cfgd, model_name, L, fig, pk, pk_src)
 
     # one engine for every scenario: cache for the batch at full context, or 64 short sequences
     decode_room = K + W + 8
@@ -254,9 +304,12 @@ def main():
 
     # ---- the same through the Python entry point: host token ids in, host token ids out, every
     # step; W warm-up steps after the prompt, then K timed steps that end at the same position
-    plen = CONTEXT - K - W - 1
+    # (the first few dozen steps after a batch of long prompts run slower while the GPU comes back from
+    # the power cap the prompts drove it into; they are warm-up here as the separate prompt phase is above)
+    We = max(W, 48)
+    plen = CONTEXT - K - We - 1
     model.generate([rand_ids(64) for _ in range(B)], max_new_tokens=4, stop_ids=[])      # compile/capture
-    res = model.generate([rand_ids(plen) for _ in range(B)], max_new_tokens=K + W + 1, stop_ids=[])
+    res = model.generate([rand_ids(plen) for _ in range(B)], max_new_tokens=K + We + 1, stop_ids=[])
     timed_steps = res.step_s[-K:]
     e2e_val = B * len(timed_steps) / sum(timed_steps)
     h2d = eng.last_upload_bytes          # token ids, positions, slots and page table of the last step

@@ -162,6 +162,10 @@ def generate_pipelined(backend, prompts: Sequence[Sequence[int]], choose: Callab
             t0 = clock()
             logits = backend.step([StepItem(slots[r], list(prompts[r]), [len(prompts[r]) - 1]) for r in batch])
             pending, pending_toks = list(batch), choose(logits, batch, [0] * len(batch), None)
+            # the copy of the tokens to the host starts behind the sampling and is waited for by
+            # itself, not by the stream (which by then holds the next step); `pending_sel` picks the
+            # sequences that are still pending out of what was copied
+            pending_read, pending_sel = _start_read(backend, pending_toks), None
             first = True
             while pending:
                 # who goes on if the token just sampled is no stop token: decided by counts alone
@@ -175,7 +179,12 @@ def generate_pipelined(backend, prompts: Sequence[Sequence[int]], choose: Callab
                     for r in cont:
                         n_fed[r] += 1
                     nxt_toks = choose(logits, cont, [n_tok[r] for r in cont], None)
-                toks = _as_list(pending_toks)                 # waits for the sampling before the step above
+                nxt_read = _start_read(backend, nxt_toks) if nxt_toks is not None else None
+                if pending_read is not None:                  # waits for the sampling before the step above
+                    toks = pending_read()
+                    toks = toks if pending_sel is None else [toks[i] for i in pending_sel]
+                else:
+                    toks = _as_list(pending_toks)
                 now = clock()
                 if first:
                     res.prefill_s += now - t0
@@ -202,15 +211,25 @@ def generate_pipelined(backend, prompts: Sequence[Sequence[int]], choose: Callab
                     else:
                         continue
                     backend.end_sequence(slots.pop(r))
+                nxt_sel = None
                 if stopped & set(cont):
                     keep = [i for i, r in enumerate(cont) if r not in stopped]
                     nxt_toks = nxt_toks[keep] if keep else None
+                    nxt_sel = keep
                     cont = [cont[i] for i in keep]
-                pending, pending_toks = cont, nxt_toks
+                pending, pending_toks, pending_read, pending_sel = cont, nxt_toks, nxt_read, nxt_sel
         finally:
             for s in slots.values():
                 backend.end_sequence(s)
     return res
+
+
+def _start_read(backend, toks):
+    """Begin the device-to-host copy of sampled tokens if the backend can do that apart from its
+    stream (`read_tokens_async(toks)` returns a function that waits for that copy alone and gives
+    the list); None otherwise."""
+    f = getattr(backend, "read_tokens_async", None)
+    return f(toks) if f is not None and toks is not None else None
 
 
 def _as_list(toks):

@@ -138,6 +138,7 @@ class Engine:
                                    self.rt)
         self.err = torch.zeros(1, dtype=torch.int32, device=dev)
         self._stages = [(None, None, None)] * 4    # (pinned tensor, its numpy view, copy-done event)
+        self._tok_bufs, self._tok_next = [None] * 4, 0   # pinned buffers for sampled tokens on their way to the host
         self._stage_next = 0
         self._graphs = {}
         self._graph_pool = None
@@ -286,6 +287,26 @@ class Engine:
         graph.replay()
         ops.count_launches(launches)
         return out.clone()
+
+    def read_tokens_async(self, toks: torch.Tensor):
+        """Start copying sampled token ids (int32, on the device) to pinned host memory behind
+        what the stream holds now; the returned function waits for that copy alone, not for work
+        queued later, and gives the ids as a list."""
+        n = int(toks.numel())
+        slot = self._tok_next
+        self._tok_next = (slot + 1) % len(self._tok_bufs)
+        buf = self._tok_bufs[slot]
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
+            self._tok_bufs[slot] = buf
+        buf[:n].copy_(toks.reshape(-1), non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+
+        def result():
+            done.synchronize()
+            return buf[:n].tolist()
+        return result
 
     def check_device_errors(self) -> None:
         """Read the kernels' error word (synchronises)."""

@@ -167,3 +167,19 @@ def test_pipelined_loop_makes_the_same_decisions(max_new, stop, max_seq):
     flat = [t for step in b.fed for t in step]
     assert all(t in {x for v in script.values() for x in v} for t in flat)
     assert got.decode_tokens + len(prompts) == sum(len(t) for t in got.tokens)
+    # a backend that hands the sampled tokens to the host by a copy of its own (started right after
+    # the sampling, read one step later, possibly after some of its sequences were dropped)
+    c = FakeBackend(max_batch=3, num_pages=12, page_size=4, max_seq_len=max_seq)
+    c.reads = 0
+
+    def read_tokens_async(toks):
+        snapshot = [int(t) for t in toks]
+
+        def result():
+            c.reads += 1
+            return snapshot
+        return result
+    c.read_tokens_async = read_tokens_async
+    again = generate_pipelined(c, prompts, tensor_script(script), max_new, stop)
+    assert again.tokens == want.tokens and again.finish == want.finish and c.len == {}
+    assert c.reads >= 1
