@@ -29,7 +29,7 @@
 // D[ra, rb] = sum_k A[ra, k] B[rb, k];  SWAP = false: C[ra * ldc + rb];  SWAP = true: C[rb * ldc + ra].
 #define TC_MAX_STAGES 12
 
-template <int BN, bool SWAP, typename TOut>
+template <int BN, bool SWAP, typename TOut, bool GATED = false>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                TOut* __restrict__ C, long long split_stride, int ldc, int RA, int RB, int k_iters_total,
@@ -137,7 +137,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (rb0 + c0 >= RB) break;   // uniform over the warp
                 float v[16];
                 tmem_ld16(tmem + ((unsigned)(quad * 32) << 16) + (unsigned)c0, v);
-                if (SWAP) {
+                if (SWAP && GATED) {
+                    // weight rows 2i, 2i + 1 are gate and up of output i: neighbouring lanes hold them,
+                    // the even lane writes silu(gate) * up (ldc = outputs per token)
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const float up = __shfl_xor_sync(0xffffffffu, v[j], 1);
+                        const int rb = rb0 + c0 + j;
+                        if (!(lane & 1) && rb < RB && ra + 1 < RA)
+                            store_out<TOut>(Cz + (size_t)rb * ldc + (ra >> 1), (v[j] / (1.0f + __expf(-v[j]))) * up);
+                    }
+                } else if (SWAP) {
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         const int rb = rb0 + c0 + j;
@@ -222,7 +232,7 @@ static int pick_stages(int stage_bytes, long long n_blocks, int k_iters_per_bloc
     return stages < 2 ? 2 : stages;
 }
 
-template <int BN, bool SWAP, typename TOut>
+template <int BN, bool SWAP, typename TOut, bool GATED = false>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TOut* C, long long split_stride, int ldc,
                      int RA, int RB, int k_iters, int splits, int* err, cudaStream_t s) {
     const int stage_bytes = TC_BM * TC_BK * 2 + BN * TC_BK * 2;
@@ -230,7 +240,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TOut* C, long
     dim3 grid((RA + TC_BM - 1) / TC_BM, (RB + BN - 1) / BN, splits);
     const int stages = pick_stages(stage_bytes, (long long)grid.x * grid.y * grid.z, per_split);
     const size_t smem = (size_t)stages * stage_bytes + 1024;
-    auto kern = gemm_tc_kernel<BN, SWAP, TOut>;
+    auto kern = gemm_tc_kernel<BN, SWAP, TOut, GATED>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     illm_launch(kern, dim3(grid), dim3(TC_THREADS), smem, s, ma, mb, C, split_stride, ldc, RA, RB, k_iters, per_split, stages, err);
@@ -294,6 +304,26 @@ extern "C" int illm_gemm_bf16_tc(const void* X, const void* W, void* out, int ou
     if (out_dtype == ILLM_BF16) return run_tc<bf16>(X, W, (bf16*)out, M, N, K, ws, splits, err, s, skip_reduce);
     if (out_dtype == ILLM_F32) return run_tc<float>(X, W, (float*)out, M, N, K, ws, splits, err, s, skip_reduce);
     return ILLM_ERR_BAD_ARG;
+}
+
+// Decode-sized product (M <= 64) of a gated feed-forward's packed weight, whose rows are gate and up
+// of an output in turn: out[M, N / 2] = silu(gate) * up in bfloat16, straight from the accumulator
+// (formula src/kern/naive/naive.cpp:80-89), without splitting K.
+extern "C" int illm_gemm_bf16_tc_gated(const void* X, const void* W, void* out, int M, int N, int K, int* err,
+                                       void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 64 || (N & 1) || K <= 0 || (K & 7) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return ILLM_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int k_iters = (K + TC_BK - 1) / TC_BK;
+    CUtensorMap ma, mb;
+    int rc;
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    if ((rc = make_map(&ma, W, N, K, TC_BM)) != 0) return rc;
+    if ((rc = make_map(&mb, X, M, K, bn)) != 0) return rc;
+    bf16* o = (bf16*)out;
+    if (bn == 16) return launch_tc<16, true, bf16, true>(ma, mb, o, 0, N / 2, N, M, k_iters, 1, err, s);
+    if (bn == 32) return launch_tc<32, true, bf16, true>(ma, mb, o, 0, N / 2, N, M, k_iters, 1, err, s);
+    return launch_tc<64, true, bf16, true>(ma, mb, o, 0, N / 2, N, M, k_iters, 1, err, s);
 }
 
 // out[i] = sum over slices (ascending) of ws[z][i]: the stand-alone form of the reduction.

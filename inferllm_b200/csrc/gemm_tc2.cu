@@ -18,8 +18,8 @@
 //                         last slice to both blocks' "accumulator full" barriers;
 //   warps 2-5 (both)      tcgen05.ld of the block's own 128 rows, conversion, stores; then an
 //                         arrival on block 0's "accumulator empty" barrier.
-// EPI 0: plain store.  EPI 1: gated activation: the weight's rows come in blocks of 128 gate rows
-// followed by their 128 up rows, a tile then holds both for 128 outputs, and the epilogue writes
+// EPI 0: plain store.  EPI 1: gated activation: the weight's rows are gate and up of an output in
+// turn, a thread of the epilogue then holds both for 8 outputs in the 16 columns it reads, and writes
 // silu(gate) * up (formula src/kern/naive/naive.cpp:80-89; the reference runs w3, w1, Silu and Mul
 // as four operators, src/core/graph.cpp:57-79), so the packed projection never goes to memory.
 // Every wait is bounded and raises the error word.
@@ -180,24 +180,23 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             tc_fence_after();
             const unsigned tbase = tmem + ((unsigned)(quad * 32) << 16) + (unsigned)(buf * T2_BN);
             if (EPI == 1) {
-                const int out0 = rb0 / 2;            // 128 outputs per 256-wide tile
+                // columns 2i, 2i + 1 of the product are gate and up of output i (ldc = outputs per row)
 #pragma unroll 1
-                for (int c0 = 0; c0 < T2_HALF; c0 += 16) {
-                    if (out0 + c0 >= ldc) break;
-                    float g[16], u[16], r[16];
-                    tmem_ld16(tbase + c0, g);
-                    tmem_ld16(tbase + T2_HALF + c0, u);
+                for (int c0 = 0; c0 < T2_BN; c0 += 16) {
+                    if (rb0 + c0 >= RB) break;
+                    float v[16], r[8];
+                    tmem_ld16(tbase + c0, v);
 #pragma unroll
-                    for (int j = 0; j < 16; j++) r[j] = (g[j] / (1.0f + __expf(-g[j]))) * u[j];
+                    for (int j = 0; j < 8; j++) r[j] = (v[2 * j] / (1.0f + __expf(-v[2 * j]))) * v[2 * j + 1];
                     if (ra < RA) {
-                        TOut* dst = C + (size_t)ra * ldc + out0 + c0;
-                        if (out0 + c0 + 16 <= ldc && ((ldc & 7) == 0)) {
+                        const int o0 = (rb0 + c0) / 2;
+                        TOut* dst = C + (size_t)ra * ldc + o0;
+                        if (o0 + 8 <= ldc && ((ldc & 7) == 0)) {
                             store8(dst, r);
-                            store8(dst + 8, r + 8);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < 16; j++)
-                                if (out0 + c0 + j < ldc) store_out<TOut>(dst + j, r[j]);
+                            for (int j = 0; j < 8; j++)
+                                if (o0 + j < ldc) store_out<TOut>(dst + j, r[j]);
                         }
                     }
                 }
@@ -291,17 +290,18 @@ static int t2_launch(const void* X, const void* W, TOut* out, int ldc, int M, in
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_illm_pdl ? 2 : 1;
+    g_illm_launches++;
     cudaLaunchKernelEx(&cfg, kern, ma, mb, out, ldc, M, N, k_iters, err);
     return illm_launch_status();
 }
 
-// C = X . W^T (epi 0, C [M, N]) or the gated activation of it (epi 1, C [M, N / 2], W's rows in
-// blocks of 128 gate rows followed by their 128 up rows).  X, W 16-byte aligned; K % 8 == 0.
+// C = X . W^T (epi 0, C [M, N]) or the gated activation of it (epi 1, C [M, N / 2], W's rows gate
+// and up of an output in turn).  X, W 16-byte aligned; K % 8 == 0.
 extern "C" int illm_gemm_bf16_tc2(const void* X, const void* W, void* out, int out_dtype, int epi, int M, int N,
                                   int K, int* err, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K & 7) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return ILLM_ERR_BAD_ARG;
-    if (epi == 1 && (N % 256)) return ILLM_ERR_BAD_ARG;
+    if (epi == 1 && (N & 1)) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     if (epi == 0 && out_dtype == ILLM_BF16) return t2_launch<0, bf16>(X, W, (bf16*)out, N, M, N, K, err, s);
     if (epi == 0 && out_dtype == ILLM_F32) return t2_launch<0, float>(X, W, (float*)out, N, M, N, K, err, s);

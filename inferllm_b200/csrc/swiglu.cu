@@ -1,5 +1,7 @@
-// Gated activation of the feed-forward: out[t, i] = silu(gu[t, i]) * gu[t, I + i], where the
-// packed projection holds the gate in its first I columns and the up projection in the next I.
+// Gated activation of the feed-forward: out[t, i] = silu(gu[t, 2i]) * gu[t, 2i + 1]: the packed
+// projection holds gate and up of an output next to each other (the weight's rows are interleaved at
+// load), so that a matrix-product epilogue that sees a few neighbouring columns can apply the same
+// formula without this kernel.
 // silu(x) = x / (1 + exp(-x)) as in the reference (src/kern/gpu/kernel_gpu.cu:183-258 runs it
 // as two launches, Silu and Mul; formula src/kern/naive/naive.cpp:80-89), in float32.
 #include "common.cuh"
@@ -9,17 +11,16 @@ __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, i
     pdl_grid_sync();
     const int t = blockIdx.y;
     const TA* g = gu + (size_t)t * 2 * I;
-    const TA* u = g + I;
     TA* o = out + (size_t)t * I;
     for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < I; c += gridDim.x * blockDim.x) {
-        float a = to_f32(g[c]);
-        float b = to_f32(u[c]);
+        float a = to_f32(g[2 * c]);
+        float b = to_f32(g[2 * c + 1]);
         float sv = a / (1.0f + expf(-a));
         o[c] = from_f32<TA>(sv * b);
     }
 }
 
-// 8 elements per thread with 16-byte loads (I a multiple of 8).
+// 8 outputs per thread from 16 consecutive inputs with 16-byte loads (I a multiple of 8).
 template <typename TA>
 __global__ void swiglu_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, long long n_vec) {
     pdl_grid_sync();
@@ -28,12 +29,12 @@ __global__ void swiglu_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ ou
     const int per_row = I / 8;
     const long long t = i / per_row;
     const int c = (int)(i - t * per_row) * 8;
-    float a[8], b[8];
-    load8(gu + t * 2 * I + c, a);
-    load8(gu + t * 2 * I + I + c, b);
+    float x[16];
+    load8(gu + t * 2 * I + 2 * c, x);
+    load8(gu + t * 2 * I + 2 * c + 8, x + 8);
     float r[8];
 #pragma unroll
-    for (int k = 0; k < 8; k++) r[k] = (a[k] / (1.0f + expf(-a[k]))) * b[k];
+    for (int k = 0; k < 8; k++) r[k] = (x[2 * k] / (1.0f + expf(-x[2 * k]))) * x[2 * k + 1];
     store8(out + t * I + c, r);
 }
 
@@ -47,20 +48,19 @@ __global__ void swiglu_partials_kernel(const float* __restrict__ slices, int P, 
     const int per_row = I / 8;
     const long long t = i / per_row;
     const int c = (int)(i - t * per_row) * 8;
-    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int z = 0; z < P; z++) {
-        float pa[8], pb[8];
-        load8(slices + (size_t)z * stride + t * 2 * I + c, pa);
-        load8(slices + (size_t)z * stride + t * 2 * I + I + c, pb);
+    float x[16];
 #pragma unroll
-        for (int k = 0; k < 8; k++) {
-            a[k] += pa[k];
-            b[k] += pb[k];
-        }
+    for (int k = 0; k < 16; k++) x[k] = 0.f;
+    for (int z = 0; z < P; z++) {
+        float px[16];
+        load8(slices + (size_t)z * stride + t * 2 * I + 2 * c, px);
+        load8(slices + (size_t)z * stride + t * 2 * I + 2 * c + 8, px + 8);
+#pragma unroll
+        for (int k = 0; k < 16; k++) x[k] += px[k];
     }
     float r[8];
 #pragma unroll
-    for (int k = 0; k < 8; k++) r[k] = (a[k] / (1.0f + expf(-a[k]))) * b[k];
+    for (int k = 0; k < 8; k++) r[k] = (x[2 * k] / (1.0f + expf(-x[2 * k]))) * x[2 * k + 1];
     store8(out + t * I + c, r);
 }
 

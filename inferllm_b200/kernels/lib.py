@@ -33,6 +33,7 @@ _SIGNATURES = {
     "illm_gemm_bf16_tc2": [P, P, P, I, I, I, I, I, P, P],
     "illm_swiglu_partials": [P, I, LL, P, I, I, P],
     "illm_gemm_bf16_tc_tune": [I],
+    "illm_gemm_bf16_tc_gated": [P, P, P, I, I, I, P, P],
     "illm_set_pdl": [I],
     "illm_launch_count": [],
     "illm_attention_prefill_tc": [P, I, I, P, P, LL, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P],

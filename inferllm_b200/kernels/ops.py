@@ -129,20 +129,43 @@ def residual_add(resid, delta):
 
 
 def swiglu(gu):
-    """gu [T, 2I] = [gate | up] -> silu(gate) * up, [T, I].  `gu` may be `SplitKPartials`."""
+    """silu(gate) * up of a packed projection [T, 2I] whose columns 2i, 2i + 1 are gate and up of
+    output i -> [T, I].  `gu` may be `SplitKPartials` (bfloat16 result)."""
     if isinstance(gu, SplitKPartials):
         T, I2 = gu.shape
-        if (I2 // 2) % 8 == 0:
+        if I2 % 16 == 0:
             out = torch.empty((T, I2 // 2), dtype=torch.bfloat16, device=gu.device)
             _check(load().illm_swiglu_partials(_ptr(gu.ws), gu.splits, gu.rows * gu.cols, _ptr(out), T, I2 // 2,
                                                _stream()), "swiglu_partials")
             return out
         gu = gu.materialize(torch.bfloat16)
-    _need(gu, "gate_up", None, 2)
+    _need(gu, "gu", None, 2)
     T, I2 = gu.shape
+    if I2 % 2:
+        raise KernelError("swiglu: the packed projection must have an even number of columns")
     out = torch.empty((T, I2 // 2), dtype=gu.dtype, device=gu.device)
     _check(load().illm_swiglu(_ptr(gu), _ptr(out), act_code(gu.dtype), T, I2 // 2, _stream()), "swiglu")
     return out
+
+
+def linear_gated(x, w):
+    """silu(gate) * up of x [M, K] . w [2I, K]^T, where w's rows 2i, 2i + 1 are the gate and the up
+    row of output i -> [M, I].  Where the package's tcgen05 kernels run the product (see
+    `set_gemm_backend`) the activation is their epilogue and the packed projection never reaches
+    memory; elsewhere it is the product followed by `swiglu`."""
+    M, K = x.shape
+    N = w.shape[0]
+    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M > 0 and K % 8 == 0 and N % 2 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        tc = _GEMM_BACKEND == "tc" or (_GEMM_BACKEND == "auto" and M <= GEMM_TC_MAX_TOKENS_AUTO)
+        if tc and M <= 64 and gemm_tc_splits(M, N, K) == 1:
+            out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+            _check(load().illm_gemm_bf16_tc_gated(_ptr(x), _ptr(w), _ptr(out), M, N, K,
+                                                  _ptr(tc_error_word(x.device)), _stream()), "gemm_bf16_tc_gated")
+            return out
+        if _GEMM_BACKEND == "tc" and M > 128 and N >= 256:
+            return gemm_bf16_tc2(x, w, torch.bfloat16, gated=True)
+    return swiglu(linear(x, w, defer_reduce=True))
 
 
 def rope_kv_write(qkv, cos_sin, rot_dim, token_pos, token_seq, block_table, k_cache, v_cache,
@@ -491,17 +514,17 @@ def set_pdl(on: bool) -> None:
 
 def gemm_bf16_tc2(x, w, out_dtype=torch.bfloat16, gated=False):
     """bfloat16 x [M, K] . w [N, K]^T on pairs of SMs (tcgen05 cta_group::2), for prompts.
-    `gated`: w's rows come in blocks of 128 gate rows followed by their 128 up rows and the result
-    is silu(gate) * up, [M, N / 2]."""
+    `gated`: w's rows 2i, 2i + 1 are the gate and the up row of output i and the result is
+    silu(gate) * up, [M, N / 2]."""
     _need(x, "x", torch.bfloat16, 2)
     _need(w, "w", torch.bfloat16, 2)
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K:
         raise KernelError(f"gemm: x is [{M}, {K}] but w is {tuple(w.shape)}")
-    if K % 8 or x.data_ptr() % 16 or w.data_ptr() % 16 or (gated and N % 256):
+    if K % 8 or x.data_ptr() % 16 or w.data_ptr() % 16 or (gated and N % 2):
         raise KernelError(f"gemm_bf16_tc2: K = {K} must be a multiple of 8, the operands 16-byte aligned"
-                          " and a gated weight a multiple of 256 rows")
+                          " and a gated weight an even number of rows")
     out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
     _check(load().illm_gemm_bf16_tc2(_ptr(x), _ptr(w), _ptr(out), act_code(out_dtype), 1 if gated else 0, M, N, K,
                                      _ptr(tc_error_word(x.device)), _stream()), "gemm_bf16_tc2")

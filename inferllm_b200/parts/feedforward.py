@@ -2,8 +2,9 @@
 
 The reference's `LlamaFFNModule` (src/core/graph.cpp:57-79) runs w3 (up), w1 (gate), Silu,
 Mul, w2 (down) as five operators; silu(x) = x / (1 + exp(-x)) (src/kern/naive/naive.cpp:80-89).
-Here gate and up are stacked into one [2I, H] matrix at load, so one product feeds the
-activation kernel.
+Here gate and up are packed into one [2I, H] matrix at load, row 2i the gate row and row 2i + 1 the
+up row of output i, so that one product feeds the activation, and where the package's own kernels run
+that product the activation is their epilogue (`kernels.ops.linear_gated`).
 """
 from __future__ import annotations
 
@@ -32,14 +33,12 @@ class GatedMLP(FeedForward):
 
     def load(self, tensors):
         dt = self.rt.dtype
-        self.w_gate_up = torch.cat([tensors["gate_proj.weight"].to(dt),
-                                    tensors["up_proj.weight"].to(dt)], dim=0).contiguous()
+        self.w_gate_up = torch.stack([tensors["gate_proj.weight"].to(dt), tensors["up_proj.weight"].to(dt)],
+                                     dim=1).reshape(2 * self.inter, self.hidden).contiguous()
         self.w_down = tensors["down_proj.weight"].to(dt).contiguous()
 
     def forward(self, h, ctx):
-        gu = ops.linear(h, self.w_gate_up, defer_reduce=True)     # the activation kernel adds K slices up
-        return ops.linear(ops.swiglu(gu), self.w_down)
+        return ops.linear(ops.linear_gated(h, self.w_gate_up), self.w_down)
 
     def forward_deferred(self, h, ctx):
-        gu = ops.linear(h, self.w_gate_up, defer_reduce=True)
-        return ops.linear(ops.swiglu(gu), self.w_down, defer_reduce=True)
+        return ops.linear(ops.linear_gated(h, self.w_gate_up), self.w_down, defer_reduce=True)

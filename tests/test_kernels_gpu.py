@@ -94,7 +94,7 @@ def test_swiglu(dtype, T, I):
     gu = (torch.randn(T, 2 * I, generator=g) * 2).to(DT[dtype])
     out = ops.swiglu(dev(gu))
     x = f64(gu)
-    ref = plain.silu(x[:, :I]) * x[:, I:]
+    ref = plain.silu(x[:, 0::2]) * x[:, 1::2]          # gate and up of an output are neighbours
     assert maxrel(f64(out), ref) <= (1e-6 if dtype == "float32" else 2 ** -8)
 
 
@@ -167,17 +167,38 @@ def test_gemm_bf16_tc2(M, N, K, out):
     assert maxrel(f64(got), ref) <= (2e-6 * math.sqrt(K) if out == "float32" else 2 ** -8)
 
 
-@pytest.mark.parametrize("M,I,K", [(300, 128, 64), (2048, 640, 328), (130, 11008, 256)])
+@pytest.mark.parametrize("M,I,K", [(300, 128, 64), (2048, 640, 328), (130, 11008, 256), (129, 100, 72)])
 def test_gemm_bf16_tc2_gated(M, I, K):
-    """Gate and up rows interleaved in blocks of 128: the epilogue applies silu(gate) * up."""
+    """Gate and up rows in turn: the epilogue of the SM-pair kernel applies silu(gate) * up."""
     g = torch.Generator().manual_seed(I)
     x = torch.randn(M, K, generator=g).bfloat16()
     wg, wu = (torch.randn(I, K, generator=g) * 0.1).bfloat16(), (torch.randn(I, K, generator=g) * 0.1).bfloat16()
-    packed = torch.stack((wg.view(I // 128, 128, K), wu.view(I // 128, 128, K)), dim=1).reshape(2 * I, K)
+    packed = torch.stack((wg, wu), dim=1).reshape(2 * I, K)
     got = ops.gemm_bf16_tc2(dev(x), dev(packed), torch.bfloat16, gated=True)
     assert tuple(got.shape) == (M, I) and int(ops.tc_error_word(got.device).item()) == 0
     ref = plain.silu(plain.linear(f64(x), f64(wg))) * plain.linear(f64(x), f64(wu))
     assert maxrel(f64(got), ref) <= 2 ** -7
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 128, 64), (8, 11008, 4096), (3, 100, 72), (16, 65, 512), (17, 300, 1000),
+                                   (64, 500, 320), (40, 1000, 2048)])
+def test_linear_gated(M, I, K):
+    """The packed gate/up product with the activation: as the epilogue of the decode-sized tcgen05
+    kernel where K is not split, through the slices where it is, after the library product
+    otherwise; all give silu(x Wg^T) * (x Wu^T)."""
+    g = torch.Generator().manual_seed(I + M)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    wg, wu = (torch.randn(I, K, generator=g) * 0.1).bfloat16(), (torch.randn(I, K, generator=g) * 0.1).bfloat16()
+    packed = dev(torch.stack((wg, wu), dim=1).reshape(2 * I, K))
+    ref = plain.silu(plain.linear(f64(x), f64(wg))) * plain.linear(f64(x), f64(wu))
+    try:
+        for backend in ("tc", "library", "auto"):
+            ops.set_gemm_backend(backend)
+            got = ops.linear_gated(dev(x), packed)
+            assert tuple(got.shape) == (M, I) and int(ops.tc_error_word(got.device).item()) == 0
+            assert maxrel(f64(got), ref) <= 2 ** -7, backend
+    finally:
+        ops.set_gemm_backend("auto")
 
 
 def test_gemm_bf16_tc_rows_do_not_depend_on_the_batch():
@@ -218,7 +239,7 @@ def test_unreduced_split_k_slices_feed_norm_and_rope():
     wg = (torch.randn(512, 4096, generator=g) * 0.05).bfloat16()
     pg = ops.gemm_bf16_tc(dev(x), dev(wg), defer_reduce=True, splits=4)
     fg = f64(pg.materialize(torch.float32))
-    assert maxrel(f64(ops.swiglu(pg)), plain.silu(fg[:, :256]) * fg[:, 256:]) <= 2 ** -7
+    assert maxrel(f64(ops.swiglu(pg)), plain.silu(fg[:, 0::2]) * fg[:, 1::2]) <= 2 ** -7
     # the packed projection of an attention layer: 3 heads + 2 x 1 kv heads of 64 channels
     nh, nkv, d, page = 3, 1, 64, 16
     wq = (torch.randn((nh + 2 * nkv) * d, 4096, generator=g) * 0.05).bfloat16()
