@@ -40,11 +40,13 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restri
         o[c] = from_f32<TA>((row[c] * scale) * to_f32(w[c]));
 }
 
-// Rows of up to 8 * 8 * 256 elements (H a multiple of 8): the row stays in registers, 8
-// elements per thread and iteration with 16-byte accesses; same arithmetic as above.
-#define RN_THREADS 256
+// Rows of up to 2 * 8 * 1024 elements (H a multiple of 8): the row stays in registers, 8
+// elements per thread and iteration with 16-byte accesses; same arithmetic as above.  The block
+// has one thread per 8 elements up to 1024 threads (a function of H alone: the order of the sums,
+// and with it every bit of the result, is the same for one row and for thousands).
+#define RN_MAX_THREADS 1024
 template <typename TA, typename TW, int ITERS>
-__global__ void __launch_bounds__(RN_THREADS)
+__global__ void __launch_bounds__(RN_MAX_THREADS)
 add_rmsnorm_reg_kernel(float* __restrict__ resid, const TA* __restrict__ delta, const TW* __restrict__ w,
                        TA* __restrict__ y, const int* __restrict__ rows, int H, float eps, int write_resid,
                        const float* __restrict__ partials, int splits, long long split_stride) {
@@ -57,7 +59,7 @@ add_rmsnorm_reg_kernel(float* __restrict__ resid, const TA* __restrict__ delta, 
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < ITERS; i++) {
-        const int c = (threadIdx.x + i * RN_THREADS) * 8;
+        const int c = (threadIdx.x + i * (int)blockDim.x) * 8;
         if (c < H) {
             load8(x + c, v[i]);
             if (dl) {
@@ -70,9 +72,20 @@ add_rmsnorm_reg_kernel(float* __restrict__ resid, const TA* __restrict__ delta, 
                 // the addend is still in K slices (float32, from a split matrix product): they are
                 // summed here, in ascending order, instead of by a kernel of their own
                 float d8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                for (int z = 0; z < splits; z++) {
+                const float* pz = partials + (size_t)r * H + c;
+                int z = 0;
+                for (; z + 4 <= splits; z += 4) {        // four slices in flight, added in order
+                    float p8[4][8];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) load8(pz + (size_t)(z + q) * split_stride, p8[q]);
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+#pragma unroll
+                        for (int k = 0; k < 8; k++) d8[k] += p8[q][k];
+                }
+                for (; z < splits; z++) {
                     float p8[8];
-                    load8(partials + (size_t)z * split_stride + (size_t)r * H + c, p8);
+                    load8(pz + (size_t)z * split_stride, p8);
 #pragma unroll
                     for (int k = 0; k < 8; k++) d8[k] += p8[k];
                 }
@@ -89,7 +102,7 @@ add_rmsnorm_reg_kernel(float* __restrict__ resid, const TA* __restrict__ delta, 
     TA* o = y + (size_t)blockIdx.x * H;
 #pragma unroll
     for (int i = 0; i < ITERS; i++) {
-        const int c = (threadIdx.x + i * RN_THREADS) * 8;
+        const int c = (threadIdx.x + i * (int)blockDim.x) * 8;
         if (c < H) {
             float w8[8], r8[8];
             load8(w + c, w8);
@@ -104,16 +117,18 @@ template <typename TA, typename TW>
 static int launch(float* resid, const void* delta, const void* w, void* y, const int* rows,
                   int n_rows, int H, float eps, int write_resid, cudaStream_t s,
                   const float* partials = nullptr, int splits = 0, long long split_stride = 0) {
-    if (partials && !((H & 7) == 0 && H <= 8 * 8 * RN_THREADS)) return ILLM_ERR_BAD_ARG;
-    if ((H & 7) == 0 && H <= 8 * 8 * RN_THREADS) {
-        const int iters = (H / 8 + RN_THREADS - 1) / RN_THREADS;
+    if (partials && !((H & 7) == 0 && H <= 2 * 8 * RN_MAX_THREADS)) return ILLM_ERR_BAD_ARG;
+    if ((H & 7) == 0 && H <= 2 * 8 * RN_MAX_THREADS) {
+        const int chunks = H / 8;
+        int threads = (chunks + 31) / 32 * 32;
+        if (threads > RN_MAX_THREADS) threads = RN_MAX_THREADS;
+        if (threads < 64) threads = 64;
+        const int iters = (chunks + threads - 1) / threads;
 #define RN_CASE(N)                                                                                   \
-    illm_launch(add_rmsnorm_reg_kernel<TA, TW, N>, dim3(n_rows), dim3(RN_THREADS), 0, s, resid, (const TA*)delta, (const TW*)w, \
+    illm_launch(add_rmsnorm_reg_kernel<TA, TW, N>, dim3(n_rows), dim3(threads), 0, s, resid, (const TA*)delta, (const TW*)w, \
                                                                    (TA*)y, rows, H, eps, write_resid, partials, splits, split_stride)
         if (iters <= 1) RN_CASE(1);
-        else if (iters <= 2) RN_CASE(2);
-        else if (iters <= 4) RN_CASE(4);
-        else RN_CASE(8);
+        else RN_CASE(2);
 #undef RN_CASE
         return illm_launch_status();
     }

@@ -21,22 +21,16 @@
 
 #include "common.cuh"
 
-__global__ void argmax_kernel(const float* __restrict__ logits, int V, int ld, int* __restrict__ out) {
-    pdl_grid_sync();
-    __shared__ float bv[32];
-    __shared__ int bi[32];
-    const float* row = logits + (size_t)blockIdx.x * ld;
-    float best = -INFINITY;
-    int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
-    }
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
-    }
+#define AM_THREADS 256
+#define AM_CHUNK 2048            // elements of a row per block of the first pass
+
+__device__ __forceinline__ void am_better(float& best, int& idx, float ov, int oi) {
+    if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+}
+// Reduces (best, idx) over the block; valid in warp 0.
+__device__ __forceinline__ void am_block(float& best, int& idx, float* bv, int* bi) {
+    for (int o = 16; o > 0; o >>= 1)
+        am_better(best, idx, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
     __syncthreads();
@@ -44,19 +38,53 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int V, int ld, i
         const int nw = blockDim.x >> 5;
         best = lane < nw ? bv[lane] : -INFINITY;
         idx = lane < nw ? bi[lane] : 0x7fffffff;
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
-        }
-        if (lane == 0) out[blockIdx.x] = (idx == 0x7fffffff) ? 0 : idx;
+        for (int o = 16; o > 0; o >>= 1)
+            am_better(best, idx, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
     }
 }
 
-extern "C" int illm_argmax(const float* logits, int B, int V, int ld, int* out, void* stream) {
+// First pass: block (c, b) finds the maximum of elements [c * AM_CHUNK, (c + 1) * AM_CHUNK) of row b.
+__global__ void __launch_bounds__(AM_THREADS)
+argmax_chunk_kernel(const float* __restrict__ logits, int V, int ld, float* __restrict__ pv, int* __restrict__ pi) {
+    pdl_grid_sync();
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    const float* row = logits + (size_t)blockIdx.y * ld;
+    const int c0 = blockIdx.x * AM_CHUNK, c1 = min(V, c0 + AM_CHUNK);
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = c0 + threadIdx.x; i < c1; i += AM_THREADS) am_better(best, idx, row[i], i);
+    am_block(best, idx, bv, bi);
+    if (threadIdx.x == 0) {
+        pv[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = best;
+        pi[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = idx;
+    }
+}
+
+// Second pass: one warp per row over the chunks' results; the lowest id among equal maxima wins,
+// whatever the order of the comparisons.
+__global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int n_chunks,
+                                    int* __restrict__ out) {
+    pdl_grid_sync();
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < n_chunks; i += 32)
+        am_better(best, idx, pv[(size_t)blockIdx.x * n_chunks + i], pi[(size_t)blockIdx.x * n_chunks + i]);
+    for (int o = 16; o > 0; o >>= 1)
+        am_better(best, idx, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
+    if (threadIdx.x == 0) out[blockIdx.x] = (idx == 0x7fffffff) ? 0 : idx;
+}
+
+// scratch_v, scratch_i: B * ceil(V / 2048) floats and ints.
+extern "C" int illm_argmax(const float* logits, int B, int V, int ld, int* out, float* scratch_v, int* scratch_i,
+                           void* stream) {
     if (B <= 0) return 0;
-    if (V <= 0) return ILLM_ERR_BAD_ARG;
-    illm_launch(argmax_kernel, dim3(B), dim3(512), 0, (cudaStream_t)stream, logits, V, ld, out);
+    if (V <= 0 || B > 65535 || scratch_v == nullptr || scratch_i == nullptr) return ILLM_ERR_BAD_ARG;
+    const int n_chunks = (V + AM_CHUNK - 1) / AM_CHUNK;
+    illm_launch(argmax_chunk_kernel, dim3(n_chunks, B), dim3(AM_THREADS), 0, (cudaStream_t)stream, logits, V, ld,
+                scratch_v, scratch_i);
+    illm_launch(argmax_final_kernel, dim3(B), dim3(32), 0, (cudaStream_t)stream, (const float*)scratch_v,
+                (const int*)scratch_i, n_chunks, out);
     return illm_launch_status();
 }
 

@@ -38,7 +38,7 @@ _SIGNATURES = {
     "illm_launch_count": [],
     "illm_attention_prefill_tc": [P, I, I, P, P, LL, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P],
     "illm_gemm_f32_nt": [P, P, P, I, I, I, I, I, I, P],
-    "illm_argmax": [P, I, I, I, P, P],
+    "illm_argmax": [P, I, I, I, P, P, P, P],
     "illm_sample": [P, I, I, I, P, P, I, F, F, I, F, P, P, P],
 }
 

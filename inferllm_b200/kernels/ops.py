@@ -569,11 +569,18 @@ def linear(x, w, out_dtype=None, defer_reduce=False):
 
 
 def argmax(logits):
-    """float32 [B, V] -> int32 [B], the lowest id among equal maxima."""
+    """float32 [B, V] -> int32 [B], the lowest id among equal maxima (two passes: chunks of 2048
+    elements, then the chunks' results)."""
     _need(logits, "logits", torch.float32, 2)
     B, V = logits.shape
     out = torch.empty((B,), dtype=torch.int32, device=logits.device)
-    _check(load().illm_argmax(_ptr(logits), B, V, V, _ptr(out), _stream()), "argmax")
+    n_chunks = -(-V // 2048)
+    for b0 in range(0, B, 65535):
+        b1 = min(B, b0 + 65535)
+        sv = torch.empty((b1 - b0, n_chunks), dtype=torch.float32, device=logits.device)
+        si = torch.empty((b1 - b0, n_chunks), dtype=torch.int32, device=logits.device)
+        _check(load().illm_argmax(_ptr(logits[b0:b1]), b1 - b0, V, V, _ptr(out[b0:b1]), _ptr(sv), _ptr(si),
+                                  _stream()), "argmax")
     return out
 
 
