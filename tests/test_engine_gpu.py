@@ -92,6 +92,31 @@ def test_whole_and_tail_one_by_one(name, dtype, model_folders, plain_logits):
     assert eng.cache.slots.n_free == eng.cache.num_slots
 
 
+@pytest.mark.parametrize("page_size", [8, 16])
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_small_pages_take_the_other_attention_kernels(name, page_size, model_folders, plain_logits):
+    """With pages of fewer than 64 positions the bfloat16 engine cannot use the TMA-fed attention
+    kernels and runs the warp-level ones instead: the same logits in every cutting."""
+    from inferllm_b200.kernels import ops
+    cfg = TINY[name]
+    assert not ops.attention_decode_ring_supported(torch.bfloat16, cfg["num_attention_heads"],
+                                                   cfg.get("num_key_value_heads", cfg["num_attention_heads"]),
+                                                   cfg["head_dim"], page_size)
+    eng = make_engine(model_folders[name], "bfloat16", max_tokens=1024, page_size=page_size)
+    ids = random_prompt(name, LENGTHS[name][0], 300)
+    ref = plain_logits(name, ids)
+    w = whole(eng, ids)
+    assert_close(w, ref, "bfloat16", f"{name} whole, pages of {page_size}")
+    t = tail_one_by_one(eng, ids)
+    assert_close(t, ref, "bfloat16", f"{name} last 32 one by one, pages of {page_size}")
+    reqs = [random_prompt(name, n, 310 + i) for i, n in enumerate([90, 33, 70])]
+    got = in_batches(eng, reqs, [60, 1, 33], [[0, 1, 2]])
+    for r, q in enumerate(reqs):
+        assert_close(got[r], plain_logits(name, q), "bfloat16", f"{name} request {r}, pages of {page_size}")
+    eng.check_device_errors()
+    eng.cache.check()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", MODELS)
 def test_unequal_batches_with_slot_reuse(name, dtype, model_folders, plain_logits):
