@@ -39,7 +39,8 @@ _SIGNATURES = {
     "illm_attention_prefill_tc": [P, I, I, P, P, LL, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P],
     "illm_gemm_f32_nt": [P, P, P, I, I, I, I, I, I, P],
     "illm_argmax": [P, I, I, I, P, P, P, P],
-    "illm_sample": [P, I, I, I, P, P, I, F, F, I, F, P, P, P],
+    "illm_sample": [P, I, I, I, P, P, I, F, F, I, F, P, P, P, P],
+    "illm_sample_scratch_elems": [I, I, I, F],
 }
 
 
@@ -66,6 +67,6 @@ def load():
             raise KernelLibraryError(f"{path} lacks the entry point {name}: rebuild with "
                                      "`python -m inferllm_b200.kernels.build --force`") from None
         fn.argtypes = args
-        fn.restype = c_longlong if name == "illm_launch_count" else c_int
+        fn.restype = c_longlong if name in ("illm_launch_count", "illm_sample_scratch_elems") else c_int
     _lib = lib
     return lib

@@ -598,7 +598,13 @@ def sample(logits, uniforms, temp, top_k=0, top_p=1.0, repeat_penalty=1.0, last_
         n_last = last_tokens.shape[1]
     z = torch.empty((B, V), dtype=torch.float32, device=logits.device)
     out = torch.empty((B,), dtype=torch.int32, device=logits.device)
-    _check(load().illm_sample(_ptr(logits), B, V, V, _ptr(z), _ptr(last_tokens), n_last, float(temp),
-                              float(repeat_penalty), int(top_k), float(top_p), _ptr(uniforms),
-                              _ptr(out), _stream()), "sample")
+    for b0 in range(0, B, 65535):
+        b1 = min(B, b0 + 65535)
+        # temperature alone and top_k <= 64 run in two passes over chunks of the row and need scratch
+        n_scratch = int(load().illm_sample_scratch_elems(b1 - b0, V, int(top_k), float(top_p)))
+        scratch = torch.empty((n_scratch,), dtype=torch.int32, device=logits.device) if n_scratch else None
+        _check(load().illm_sample(_ptr(logits[b0:b1]), b1 - b0, V, V, _ptr(z[b0:b1]),
+                                  _ptr(last_tokens[b0:b1]) if last_tokens is not None else None, n_last, float(temp),
+                                  float(repeat_penalty), int(top_k), float(top_p), _ptr(uniforms[b0:b1]),
+                                  _ptr(out[b0:b1]), _ptr(scratch), _stream()), "sample")
     return out

@@ -731,6 +731,47 @@ def test_sample_distribution_matches_the_reference_sampler(temp, top_k, top_p, p
     assert one[0] == out[1234]
 
 
+@pytest.mark.parametrize("V", [5000, 32000, 128256])
+@pytest.mark.parametrize("temp,top_k,top_p,pen", [(0.9, 0, 1.0, 1.0), (0.1, 40, 0.95, 1.3), (1.0, 64, 1.0, 1.0),
+                                                  (0.7, 8, 0.6, 1.2), (0.8, 100, 0.9, 1.0), (1.0, 0, 0.8, 1.0)])
+def test_sample_over_a_large_vocabulary(V, temp, top_k, top_p, pen):
+    """Vocabularies of several chunks: the two-pass kernels (temperature alone, top_k <= 64) and the
+    one-block kernel (the rest) against the reference's algorithm, by the frequencies of the ids
+    drawn with a fine grid of uniform numbers."""
+    N = 4000
+    g = torch.Generator().manual_seed(V + top_k)
+    logits = torch.randn(V, generator=g) * 3
+    logits[V - 3] = 9.0                       # mass at the end of the last, partial chunk
+    logits[2049] = 8.5
+    last = [2049, 7, V - 3, 7, -1]
+    ids, probs = plain.sample_distribution(logits.numpy(), [t for t in last if t >= 0], pen, top_k, top_p, temp)
+    want = np.zeros(V)
+    want[ids] = probs
+    u = (torch.arange(N, dtype=torch.float32) + 0.5) / N
+    lg = dev(logits.repeat(N, 1))
+    lt = dev(torch.tensor(last, dtype=torch.int32).repeat(N, 1))
+    out = ops.sample(lg, dev(u), temp, top_k, top_p, pen, lt).cpu().numpy()
+    freq = np.bincount(out, minlength=V) / N
+    assert set(np.nonzero(freq)[0]) <= set(ids.tolist()), "an id outside the kept set was drawn"
+    assert np.abs(freq - want).max() <= 2.0 / N + 2e-4
+    one = ops.sample(lg[:1], dev(u[1234:1235]), temp, top_k, top_p, pen, lt[:1]).cpu().numpy()
+    assert one[0] == out[1234]
+
+
+def test_sample_with_many_equal_values_takes_the_slow_way_and_stays_right():
+    """More equal values at the cut than a chunk hands on: the row is flagged and done by the
+    one-block kernel; all equals of the cut are kept, as that kernel keeps them."""
+    V, N = 6000, 3000
+    logits = torch.full((V,), -5.0)
+    logits[100:400] = 2.0                     # 300 equal maxima in one chunk
+    logits[4500] = 1.0
+    u = (torch.arange(N, dtype=torch.float32) + 0.5) / N
+    out = ops.sample(dev(logits.repeat(N, 1)), dev(u), 1.0, 10, 1.0, 1.0, None).cpu().numpy()
+    freq = np.bincount(out, minlength=V) / N
+    assert set(np.nonzero(freq)[0]) <= set(range(100, 400))
+    assert np.abs(freq[100:400] - 1 / 300).max() <= 2.0 / N
+
+
 def test_sample_large_vocabulary_and_greedy_limit():
     V = 128256
     g = torch.Generator().manual_seed(9)
