@@ -147,9 +147,8 @@ class Model:
         if stop_ids is None:
             stop_ids = [] if self.end_token is None else [self.end_token]
         sampler = Sampler(self.sampling)
-        # without a repetition penalty the sampler needs no token history on the host, and the
-        # loop can keep the host one step behind the device
-        loop = generate_pipelined if self.sampling.repeat_penalty == 1.0 else generate
-        res = loop(self.engine, prompts, sampler.choose, max_new_tokens, stop_ids, on_token)
+        # the loop that keeps the host one step behind the device; the sampler keeps the windows of
+        # last tokens for the repetition penalty on the device
+        res = generate_pipelined(self.engine, prompts, sampler.choose, max_new_tokens, stop_ids, on_token)
         self.engine.check_device_errors()
         return res

@@ -145,8 +145,9 @@ def generate_pipelined(backend, prompts: Sequence[Sequence[int]], choose: Callab
     and launching a step) no longer adds to the time per token.  A sequence that turns out to have
     sampled a stop token has then already been run one step too far: that step's result for it is
     dropped and its slot is freed, which changes nothing for the others (a sequence's logits do
-    not depend on the rest of its batch).  `choose` must return a device tensor and must not need
-    the histories (no repetition penalty): `generate` is the loop for everything else."""
+    not depend on the rest of its batch).  `choose` gets the prompts as histories with the first
+    call of a batch and None afterwards: a sampler that needs the last tokens (repetition penalty)
+    keeps them itself from there (`sampling.Sampler` does, on the device)."""
     limits: Limits = backend.limits()
     stop = set(int(s) for s in stop_ids)
     n = len(prompts)
@@ -161,7 +162,10 @@ def generate_pipelined(backend, prompts: Sequence[Sequence[int]], choose: Callab
         try:
             t0 = clock()
             logits = backend.step([StepItem(slots[r], list(prompts[r]), [len(prompts[r]) - 1]) for r in batch])
-            pending, pending_toks = list(batch), choose(logits, batch, [0] * len(batch), None)
+            # (the prompts go with the first call: a sampler that penalises repetitions starts its
+            # windows of last tokens from them and keeps them on the device from then on)
+            pending, pending_toks = list(batch), choose(logits, batch, [0] * len(batch),
+                                                        [list(prompts[r]) for r in batch])
             # the copy of the tokens to the host starts behind the sampling and is waited for by
             # itself, not by the stream (which by then holds the next step); `pending_sel` picks the
             # sequences that are still pending out of what was copied

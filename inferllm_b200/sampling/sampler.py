@@ -60,11 +60,33 @@ def uniform_for(seed: int, request: int, step: int) -> float:
 class Sampler:
     """Chooses one token per row of logits.  `histories[i]` is the list of tokens (prompt and
     generated) of row i's sequence, `requests[i]` its request number, `steps[i]` how many tokens
-    it has generated so far."""
+    it has generated so far.
+
+    For the repetition penalty the sampler needs each sequence's last `repeat_last_n` tokens.  A
+    loop that has them on the host passes `histories` with every call.  A loop that keeps the
+    sampled tokens on the device (`generate_pipelined`) passes the prompts as `histories` with the
+    first call of a batch (all `steps` 0) and None afterwards: the sampler then keeps the windows
+    on the device itself, one row per request, and writes every token it samples into them (the
+    sequences of a batch advance together, so the oldest entry of every row is at the same place)."""
 
     def __init__(self, params: SamplingParams):
         params.validate()
         self.params = params
+        self._window = None          # int32 [requests of the batch, repeat_last_n] on the device
+        self._row_of = {}            # request -> its row of the window
+
+    def _wants_history(self) -> bool:
+        return self.params.repeat_penalty != 1.0 and self.params.repeat_last_n > 0
+
+    def _start_windows(self, requests, histories, device):
+        n = self.params.repeat_last_n
+        arr = np.full((len(requests), n), -1, dtype=np.int32)
+        for i, h in enumerate(histories):
+            tail = list(h[-n:])
+            if tail:
+                arr[i, n - len(tail):] = tail          # oldest first: entry 0 is the first to be replaced
+        self._window = torch.from_numpy(arr).to(device)
+        self._row_of = {r: i for i, r in enumerate(requests)}
 
     def choose(self, logits: torch.Tensor, requests: Sequence[int], steps: Sequence[int],
                histories: Optional[Sequence[List[int]]] = None) -> torch.Tensor:
@@ -72,17 +94,39 @@ class Sampler:
         if p.greedy and p.repeat_penalty == 1.0:
             return ops.argmax(logits)
         B = logits.shape[0]
-        last = None
-        if p.repeat_penalty != 1.0 and p.repeat_last_n > 0 and histories is not None:
-            arr = np.full((B, p.repeat_last_n), -1, dtype=np.int32)
-            for i, h in enumerate(histories):
-                tail = h[-p.repeat_last_n:]
-                arr[i, :len(tail)] = tail
-            last = torch.from_numpy(arr).to(logits.device)
+        last, on_device, rows = None, False, None
+        if self._wants_history():
+            if histories is not None and all(s == 0 for s in steps) and len(set(steps)) <= 1:
+                # (also what a host-side loop passes at its first step: the windows then simply
+                # mirror what it keeps passing)
+                self._start_windows(requests, histories, logits.device)
+            if histories is not None:
+                arr = np.full((B, p.repeat_last_n), -1, dtype=np.int32)
+                for i, h in enumerate(histories):
+                    tail = h[-p.repeat_last_n:]
+                    arr[i, :len(tail)] = tail
+                last = torch.from_numpy(arr).to(logits.device)
+            elif self._window is not None and all(r in self._row_of for r in requests):
+                idx = [self._row_of[r] for r in requests]
+                rows = None if idx == list(range(self._window.shape[0])) else torch.tensor(idx, device=logits.device)
+                last = self._window if rows is None else self._window[rows]
+                on_device = True
         if p.greedy:
             # greedy with a repetition penalty: the penalised maximum; top_k = 1 keeps exactly it
             u = torch.zeros(B, dtype=torch.float32, device=logits.device)
-            return ops.sample(logits, u, 1.0, 1, 1.0, p.repeat_penalty, last)
-        u = torch.tensor([uniform_for(p.seed, r, s) for r, s in zip(requests, steps)],
-                         dtype=torch.float32).to(logits.device)
-        return ops.sample(logits, u, p.temp, p.top_k, p.top_p, p.repeat_penalty, last)
+            toks = ops.sample(logits, u, 1.0, 1, 1.0, p.repeat_penalty, last)
+        else:
+            u = torch.tensor([uniform_for(p.seed, r, s) for r, s in zip(requests, steps)],
+                             dtype=torch.float32).to(logits.device)
+            toks = ops.sample(logits, u, p.temp, p.top_k, p.top_p, p.repeat_penalty, last)
+        if self._wants_history() and self._window is not None and (on_device or histories is not None) \
+                and all(r in self._row_of for r in requests):
+            # the new token takes the place of the window's oldest entry
+            col = int(steps[0]) % p.repeat_last_n
+            if rows is None and len(requests) == self._window.shape[0]:
+                self._window[:, col] = toks
+            else:
+                idx = rows if rows is not None else torch.tensor([self._row_of[r] for r in requests],
+                                                                 device=logits.device)
+                self._window[idx, col] = toks
+        return toks

@@ -114,6 +114,26 @@ def test_repeat_penalty_changes_greedy_choice(model_folders, plain_models):
     assert m.generate([prompt], max_new_tokens=1, stop_ids=[]).tokens[0][0] == int(np.argmax(logits))
 
 
+@pytest.mark.parametrize("temp", [0.0, 0.9])
+def test_repeat_penalty_with_the_windows_on_the_device(temp, model_folders):
+    """The loop that keeps the host a step behind lets the sampler keep the last tokens on the
+    device; it must choose what the plain loop chooses, which passes the histories from the host
+    at every step (unequal prompts, a window shorter than some prompts, sequences ending early)."""
+    from inferllm_b200.engine import generate, generate_pipelined
+    from inferllm_b200.sampling import Sampler
+    name = "B"
+    prompts = [random_prompt(name, n, 70 + n) for n in (1, 9, 30, 17)]
+    m = load(model_folders[name], "float32", nr_ctx=256, max_tokens=1024)
+    m.init(top_k=20, top_p=0.9, temp=temp, repeat_penalty=1.4, repeat_last_n=12, seed=5, end_token=-1)
+    want = generate(m.engine, prompts, Sampler(m.sampling).choose, 25, [])
+    stop = [want.tokens[2][6]]                       # a token request 2 really samples: it ends early
+    want = generate(m.engine, prompts, Sampler(m.sampling).choose, 25, stop)
+    got = generate_pipelined(m.engine, prompts, Sampler(m.sampling).choose, 25, stop)
+    assert got.tokens == want.tokens and got.finish == want.finish
+    assert "stop" in got.finish and "length" in got.finish
+    assert m.generate(prompts, max_new_tokens=25, stop_ids=stop).tokens == want.tokens
+
+
 def test_command_line(model_folders, plain_models, tmp_path):
     name = "A"
     cfg, w = plain_models[name]
