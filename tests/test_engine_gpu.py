@@ -234,3 +234,35 @@ def test_all_products_on_the_package_kernels(name, model_folders, plain_logits):
         eng.check_device_errors()
     finally:
         ops.set_gemm_backend("auto")
+
+
+def test_layers_of_real_width_bfloat16_against_float32():
+    """Two layers with the widths of an 8B model (4096 wide, 32 heads over 8 KV heads of 128, a
+    14336-wide feed-forward, 128256 words): the bfloat16 engine with its tensor-core kernels at the
+    sizes they were written for, against the true float32 engine on the same random weights, whole,
+    token by token and in an unequal batch."""
+    from inferllm_b200 import Engine, EngineOptions, config_from_dict
+    cfg = config_from_dict(dict(architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidden_layers=2,
+                                num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                                intermediate_size=14336, vocab_size=128256, rope_theta=500000.0,
+                                rms_norm_eps=1e-5, max_position_embeddings=1024))
+    g = torch.Generator().manual_seed(17)
+    reqs = [torch.randint(0, 128256, (n,), generator=g).tolist() for n in (200, 70, 129)]
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_config(cfg, EngineOptions(dtype=dtype, max_tokens=1024, max_batch=3), 3)
+        w = whole(eng, reqs[0])
+        t = tail_one_by_one(eng, reqs[0])
+        b = in_batches(eng, reqs, [150, 70, 1], [[0, 1, 2]])
+        got[dtype] = (w, t, b)
+        eng.check_device_errors()
+        eng.cache.check()
+        del eng
+        torch.cuda.empty_cache()
+    w32, t32, b32 = got["float32"]
+    w16, t16, b16 = got["bfloat16"]
+    assert np.array_equal(w32, t32) and np.array_equal(w32, b32[0])
+    assert_close(w16, w32, "bfloat16", "whole, real widths")
+    assert_close(t16, w32, "bfloat16", "last 32 one by one, real widths")
+    for r in range(3):
+        assert_close(b16[r], b32[r], "bfloat16", f"request {r} in a batch, real widths")
