@@ -395,7 +395,6 @@ def attention(qkv, kv, ctx, n_heads, n_kv_heads, head_dim, window, scale):
         return attention_decode_ring(qkv, kv.k, kv.v, kv.block_table, ctx.token_pos, ctx.token_seq,
                                      n_heads, n_kv_heads, head_dim, kv.page_size, window, scale,
                                      ctx.max_seq_len)
-    group = n_heads // n_kv_heads if n_kv_heads else 0
     if ctx.is_decode and (group >= GQA_DECODE_MIN_GROUP or not attention_decode_supported(
             qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_size)) and attention_decode_gqa_supported(
             qkv.dtype, n_heads, n_kv_heads, head_dim):
@@ -403,8 +402,6 @@ def attention(qkv, kv, ctx, n_heads, n_kv_heads, head_dim, window, scale):
                                     n_heads, n_kv_heads, head_dim, kv.page_size, window, scale,
                                     ctx.max_seq_len)
     if ctx.is_decode and attention_decode_supported(qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_size):
-        # grid and scratch are sized for the longest sequence the cache allows, so that the
-        # launch is the same at every step
         return attention_decode(qkv, kv.k, kv.v, kv.block_table, ctx.token_pos, ctx.token_seq,
                                 n_heads, n_kv_heads, head_dim, kv.page_size, window, scale,
                                 ctx.max_seq_len)
