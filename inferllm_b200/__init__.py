@@ -13,9 +13,23 @@ from .registry import (config_from_dict, config_from_folder, get_architecture,
 from .sampling import Sampler, SamplingParams
 from .weights import WeightError, write_random_model
 
+
+def library_errors():
+    """The exception classes with which the library refuses something it was asked for (a bad
+    configuration, weights that do not fit, a request the cache or the kernels cannot take): what a
+    command line reports in one line instead of a traceback."""
+    from .cache import CacheError
+    from .engine.generate import RequestTooLong
+    from .kernels.lib import KernelLibraryError
+    from .kernels.ops import KernelError
+    from .weights.safetensors_io import SafetensorsError
+    return (ConfigError, WeightError, SafetensorsError, EngineError, CacheError, RequestTooLong, KernelError,
+            KernelLibraryError)
+
+
 __all__ = ["ConfigError", "LlamaConfig", "Engine", "EngineError", "EngineOptions",
            "GenerationResult", "Model", "ModelConfig", "StepItem", "generate", "config_from_dict",
            "config_from_folder", "get_architecture", "register_architecture",
            "registered_architectures", "Sampler", "SamplingParams", "WeightError",
-           "write_random_model"]
+           "write_random_model", "library_errors"]
 __version__ = "0.1.0"

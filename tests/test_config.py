@@ -141,3 +141,19 @@ def test_registering_another_architecture():
     finally:
         unregister_architecture("ToyForCausalLM")
     assert "ToyForCausalLM" not in registered_architectures()
+
+
+def test_command_lines_report_refusals_in_one_line(tmp_path):
+    """A model folder that is not one: exit code 1 and one line on standard error, no traceback."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for prog, args in (("llama", ["-m", str(tmp_path), "--prompt-ids", "1,2"]),
+                       ("trace_run", ["--model", str(tmp_path), "--dtype", "float32", "--out", str(tmp_path / "o"),
+                                      "--max-tokens", "64"])):
+        r = subprocess.run([sys.executable, os.path.join(root, "bin", prog)] + args, capture_output=True, text=True,
+                           stdin=subprocess.DEVNULL, timeout=300)
+        assert r.returncode == 1, (prog, r.stderr)
+        lines = [ln for ln in r.stderr.splitlines() if ln.strip()]
+        assert len(lines) == 1 and lines[0].startswith(f"{prog}: error:") and "config.json" in lines[0], r.stderr
