@@ -63,25 +63,81 @@ template <int D> __device__ __forceinline__ int rd_qswz(int r, int c) { return r
 
 }  // namespace
 
+// The position encoding and the cache write done by this kernel itself (FUSE): the packed projection
+// [T, (nh + 2 nkv) d] comes unrotated, in bfloat16 or as the float32 K slices of a split matrix
+// product, and the kernel does what rope_kv.cu does for one token: it rotates the query heads on
+// their way into shared memory, and the block that owns the token's last tile rotates the new K row,
+// writes it and the V row to the cache page and puts them into the tile it has just loaded.  The
+// arithmetic and the rounding are those of rope_kv.cu.
+struct RdRope {
+    const float* partials;     // K slices [splits][T][width], or nullptr: the bfloat16 projection is read
+    int splits;
+    long long split_stride;
+    const float2* cs;          // cos/sin table [positions][rot / 2]
+    int rot, table_positions;
+    bf16* kc;                  // the cache entry, for the write of the new row
+    bf16* vc;
+    int write_kv;
+    int* err;                  // the step's error word: 2 no page, 3 position outside the table
+};
+
+// 8 channels (chunk c) of head slot `slot` of token t, position-encoded if the chunk is rotated
 template <int D>
-__global__ void __launch_bounds__(RD_THREADS)
+__device__ __forceinline__ void rd_encoded_chunk(const RdRope& rp, const bf16* __restrict__ qkv, size_t row_off, int slot,
+                                                 int c, int p, float* out) {
+    auto fetch = [&](int cc, float* o8) {
+        const size_t off = row_off + (size_t)slot * D + cc * 8;
+        if (rp.partials) {
+#pragma unroll
+            for (int k = 0; k < 8; k++) o8[k] = 0.f;
+            for (int z = 0; z < rp.splits; z++) {
+                float p8[8];
+                load8(rp.partials + (size_t)z * rp.split_stride + off, p8);
+#pragma unroll
+                for (int k = 0; k < 8; k++) o8[k] += p8[k];
+            }
+        } else {
+            load8(qkv + off, o8);
+        }
+    };
+    const int hc = rp.rot >> 4;            // chunks per rotated half
+    if (c < 2 * hc) {
+        const int cp = c < hc ? c : c - hc;
+        float a[8], b[8];
+        fetch(cp, a);
+        fetch(cp + hc, b);
+        const float2* cst = rp.cs + (size_t)p * (rp.rot >> 1) + cp * 8;
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const float2 cc = cst[k];
+            out[k] = c < hc ? a[k] * cc.x - b[k] * cc.y : a[k] * cc.y + b[k] * cc.x;
+        }
+    } else {
+        fetch(c, out);
+    }
+}
+
+template <int D, bool FUSE>
+__global__ void __launch_bounds__(RD_THREADS + 32)
 attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                              const bf16* __restrict__ q, int q_stride, const int* __restrict__ block_table,
                              int max_pages, const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                              float* __restrict__ part_acc, float* __restrict__ part_ml, bf16* __restrict__ out,
                              int n_splits, int nh, int nkv, int G, int page_size, int window, float scale_log2e,
-                             int* __restrict__ err) {
+                             int* __restrict__ err, const RdRope rp) {
     constexpr int STAGES = 384 / D;
     constexpr int CH = D / 8, KS = D / 16, NT_D = D / 8;
     constexpr unsigned TILE_BYTES = RD_BN * D * 2;            // a K tile, or a V tile
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) unsigned long long bars[2 * STAGES];
+    __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
+    __shared__ __align__(16) bf16 new_row_s[2 * D];         // FUSE: the token's new K row, then its V row
 
     const unsigned raw = tc_smem_u32(smem_raw);
     const unsigned base = (raw + 1023u) & ~1023u;             // the swizzle's period
     unsigned char* gbase = smem_raw + (base - raw);
     bf16* Qs = reinterpret_cast<bf16*>(gbase + (size_t)STAGES * 2 * TILE_BYTES);   // [16][D]
     const unsigned full0 = tc_smem_u32(&bars[0]), empty0 = tc_smem_u32(&bars[STAGES]);
+    const unsigned row_ready = tc_smem_u32(&bars[2 * STAGES]);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
@@ -89,9 +145,11 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, RD_CONSUMERS);
         }
+        mbar_init(row_ready, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    __syncthreads();          // the barriers exist; from here the warps go their own ways
     pdl_grid_sync();
 
     const int split = blockIdx.x, hk = blockIdx.y, t = blockIdx.z;
@@ -110,15 +168,48 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
         return;
     }
 
-    // ---- Q: the G heads of this kv head as rows 0..G-1, zero rows above
-    for (int i = tid; i < 16 * CH; i += RD_THREADS) {
-        const int r = i / CH, c = i % CH;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r < G) v = *reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + (size_t)(hk * G + r) * D + c * 8);
-        *reinterpret_cast<uint4*>(Qs + rd_qswz<D>(r, c)) = v;
+    int p_tab = p;                                    // the position, kept inside the cos/sin table
+    if (FUSE && rp.rot > 0 && p >= rp.table_positions) {
+        if (tid == 0) atomicExch(rp.err, 3);
+        p_tab = rp.table_positions - 1;
     }
-    __syncthreads();
+    // FUSE: the block that owns the token's last tile also makes the token's new K and V rows
+    const bool new_row_here = FUSE && rp.write_kv && split == (tile_hi - tile_lo) % n_splits;
 
+    if (warp == RD_CONSUMERS + 1) {
+        // ---- (FUSE) the helper warp: lane < CH makes a chunk of the new K row (rotated), the next CH
+        // lanes a chunk of the V row; they go to the cache page and to shared memory, from where the
+        // consumer warp that owns the row's place in the last tile takes them
+        if (new_row_here) {
+            if (lane < 2 * CH) {
+                const bool is_k = lane < CH;
+                const int c = is_k ? lane : lane - CH;
+                float f[8];
+                if (is_k) {
+                    rd_encoded_chunk<D>(rp, q, (size_t)t * q_stride, nh + hk, c, p_tab, f);
+                } else {
+                    RdRope plain = rp;
+                    plain.rot = 0;
+                    rd_encoded_chunk<D>(plain, q, (size_t)t * q_stride, nh + nkv + hk, c, p_tab, f);
+                }
+                uint4 v;
+                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+                for (int k = 0; k < 4; k++) h2[k] = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+                *reinterpret_cast<uint4*>(new_row_s + (is_k ? 0 : D) + c * 8) = v;
+                const int page = block_table[(size_t)token_seq[t] * max_pages + p / page_size];
+                if (page < 0) {
+                    atomicExch(rp.err, 2);
+                } else {
+                    bf16* dst = (is_k ? rp.kc : rp.vc) + (((size_t)page * nkv + hk) * page_size + (p % page_size)) * D + c * 8;
+                    *reinterpret_cast<uint4*>(dst) = v;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) rd_arrive(row_ready);
+        }
+        return;
+    }
     if (warp == RD_CONSUMERS) {
         // ---- producer
         if (lane == 0) {
@@ -145,7 +236,21 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
         return;
     }
 
-    // ---- consumers: warp w owns keys 16w .. 16w+15 of every tile
+    // ---- consumers.  Q: the G heads of this kv head as rows 0..G-1, zero rows above
+    for (int i = tid; i < 16 * CH; i += RD_CONSUMERS * 32) {
+        const int r = i / CH, c = i % CH;
+        if (FUSE && r < G) {
+            float f[8];
+            rd_encoded_chunk<D>(rp, q, (size_t)t * q_stride, hk * G + r, c, p_tab, f);
+            store8(Qs + rd_qswz<D>(r, c), f);
+        } else {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < G) v = *reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + (size_t)(hk * G + r) * D + c * 8);
+            *reinterpret_cast<uint4*>(Qs + rd_qswz<D>(r, c)) = v;
+        }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(RD_CONSUMERS * 32) : "memory");
+    // warp w owns keys 16w .. 16w+15 of every tile
     const int g = lane >> 2, t4 = lane & 3, mtx = lane >> 3;
     unsigned qf[KS][4];
 #pragma unroll
@@ -165,6 +270,18 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
         alive = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, (i / STAGES) & 1, err));
         if (!alive) break;
         const int key0 = (tile_lo + split + i * n_splits) * RD_BN + warp * 16;
+        if (new_row_here && i == n_my - 1 && warp == ((p & (RD_BN - 1)) >> 4)) {
+            // the tile came from the cache before the row of position p was there (or while it was
+            // being written): this warp, the only reader of that row, puts in what the helper warp made
+            alive = __all_sync(0xffffffffu, mbar_wait(row_ready, 0, err));
+            if (lane < 2 * CH) {
+                const int c = lane < CH ? lane : lane - CH;
+                unsigned char* tile = gbase + (size_t)s * 2 * TILE_BYTES + (lane < CH ? 0 : TILE_BYTES);
+                *reinterpret_cast<uint4*>(tile + rd_tile_off(p & (RD_BN - 1), c)) =
+                    *reinterpret_cast<const uint4*>(new_row_s + (lane < CH ? 0 : D) + c * 8);
+            }
+            __syncwarp();
+        }
         if (key0 <= p && key0 + 15 >= lo) {
             const unsigned kbase = base + (unsigned)s * 2 * TILE_BYTES, vbase = kbase + TILE_BYTES;
             // two accumulator sets shorten the chain of dependent MMAs
@@ -357,7 +474,7 @@ template <int D>
 static int rd_launch(const void* q, int q_stride, const void* kc, const void* vc, long long n_pages,
                      const int* block_table, int max_pages, const int* token_pos, const int* token_seq,
                      float* part_acc, float* part_ml, void* out, int T, int nh, int nkv, int page_size, int window,
-                     float scale, int n_splits, int* err, cudaStream_t s) {
+                     float scale, int n_splits, int* err, cudaStream_t s, const RdRope* rope) {
     CUtensorMap mk, mv;
     int rc;
     const long long rows = n_pages * nkv * page_size;
@@ -365,17 +482,41 @@ static int rd_launch(const void* q, int q_stride, const void* kc, const void* vc
     if ((rc = rd_make_map(&mv, vc, rows, D)) != 0) return rc;
     constexpr int STAGES = 384 / D;
     const size_t smem = (size_t)STAGES * 2 * RD_BN * D * 2 + (size_t)16 * D * 2 + 1024;
-    auto kern = attention_decode_ring_kernel<D>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    illm_launch(kern, dim3(n_splits, nkv, T), dim3(RD_THREADS), smem, s, mk, mv, (const bf16*)q, q_stride, block_table,
-                max_pages, token_pos, token_seq, part_acc, part_ml, (bf16*)out, n_splits, nh, nkv, nh / nkv, page_size,
-                window, scale * 1.4426950408889634f, err);
-    rc = illm_launch_status();
+    RdRope rp = {};
+    if (rope) rp = *rope;
+    auto launch = [&](auto kern) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        illm_launch(kern, dim3(n_splits, nkv, T), dim3(rope ? RD_THREADS + 32 : RD_THREADS), smem, s, mk, mv, (const bf16*)q, q_stride,
+                    block_table, max_pages, token_pos, token_seq, part_acc, part_ml, (bf16*)out, n_splits, nh, nkv,
+                    nh / nkv, page_size, window, scale * 1.4426950408889634f, err, rp);
+        return illm_launch_status();
+    };
+    rc = rope ? launch(attention_decode_ring_kernel<D, true>) : launch(attention_decode_ring_kernel<D, false>);
     if (rc != 0 || n_splits == 1) return rc;
     illm_launch(attention_decode_ring_merge_kernel<D>, dim3(nh, T), dim3(D), 0, s, (const float*)part_acc,
                 (const float*)part_ml, (bf16*)out, n_splits, nh);
     return illm_launch_status();
+}
+
+static int rd_run(const void* q, int q_stride, const void* kc, const void* vc, long long n_pages,
+                  const int* block_table, int max_pages, const int* token_pos, const int* token_seq, float* part_acc,
+                  float* part_ml, void* out, int T, int nh, int nkv, int d, int page_size, int window, float scale,
+                  int n_splits, int* err, void* stream, const RdRope* rope) {
+    if (T <= 0) return 0;
+    if (nkv <= 0 || nh % nkv || nh / nkv > 16 || T > 65535 || nkv > 65535 || (q_stride & 7) || page_size % RD_BN ||
+        n_splits < 1 || n_splits > RD_MAX_SPLITS || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) ||
+        n_pages * nkv * page_size > 0x7fffffffLL || (n_splits > 1 && (part_acc == nullptr || part_ml == nullptr)))
+        return ILLM_ERR_BAD_ARG;
+    if (!(rope && rope->partials) && (q == nullptr || ((uintptr_t)q & 15))) return ILLM_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (d == 128)
+        return rd_launch<128>(q, q_stride, kc, vc, n_pages, block_table, max_pages, token_pos, token_seq, part_acc,
+                              part_ml, out, T, nh, nkv, page_size, window, scale, n_splits, err, s, rope);
+    if (d == 64)
+        return rd_launch<64>(q, q_stride, kc, vc, n_pages, block_table, max_pages, token_pos, token_seq, part_acc,
+                             part_ml, out, T, nh, nkv, page_size, window, scale, n_splits, err, s, rope);
+    return ILLM_ERR_BAD_ARG;
 }
 
 // q: the packed projection [T, q_stride] whose first nh*d columns are the query heads; kc, vc: one
@@ -386,18 +527,29 @@ extern "C" int illm_attention_decode_ring(const void* q, int q_stride, const voi
                                           const int* token_pos, const int* token_seq, float* part_acc,
                                           float* part_ml, void* out, int T, int nh, int nkv, int d, int page_size,
                                           int window, float scale, int n_splits, int* err, void* stream) {
-    if (T <= 0) return 0;
-    if (nkv <= 0 || nh % nkv || nh / nkv > 16 || T > 65535 || nkv > 65535 || (q_stride & 7) || page_size % RD_BN ||
-        n_splits < 1 || n_splits > RD_MAX_SPLITS || ((uintptr_t)q & 15) || ((uintptr_t)kc & 15) ||
-        ((uintptr_t)vc & 15) || n_pages * nkv * page_size > 0x7fffffffLL ||
-        (n_splits > 1 && (part_acc == nullptr || part_ml == nullptr)))
+    return rd_run(q, q_stride, kc, vc, n_pages, block_table, max_pages, token_pos, token_seq, part_acc, part_ml, out, T,
+                  nh, nkv, d, page_size, window, scale, n_splits, err, stream, nullptr);
+}
+
+// The same with the position encoding and the cache write inside: `qkv` is the unrotated packed
+// projection [T, (nh + 2 nkv) d] in bfloat16, or nullptr with `partials`, its `splits` float32 K
+// slices [splits][T][(nh + 2 nkv) d].  cos_sin: float32 [table_positions][rot / 2][2] (rot = 0: no
+// rotation).  write_kv = 0: the cache already holds this token's K and V (a layer that reads another
+// layer's entry).  step_err: the step's error word (2: a sequence without a page for its position,
+// 3: a position outside the table).  Needs rot % 16 == 0.
+extern "C" int illm_attention_decode_ring_rope(const void* qkv, const float* partials, int splits,
+                                               long long split_stride, const float* cos_sin, int rot,
+                                               int table_positions, int write_kv, void* kc, void* vc,
+                                               long long n_pages, const int* block_table, int max_pages,
+                                               const int* token_pos, const int* token_seq, float* part_acc,
+                                               float* part_ml, void* out, int T, int nh, int nkv, int d,
+                                               int page_size, int window, float scale, int n_splits, int* err,
+                                               int* step_err, void* stream) {
+    if (rot < 0 || rot > d || (rot & 15) || (rot > 0 && cos_sin == nullptr) || step_err == nullptr ||
+        (partials != nullptr && splits < 1))
         return ILLM_ERR_BAD_ARG;
-    cudaStream_t s = (cudaStream_t)stream;
-    if (d == 128)
-        return rd_launch<128>(q, q_stride, kc, vc, n_pages, block_table, max_pages, token_pos, token_seq, part_acc,
-                              part_ml, out, T, nh, nkv, page_size, window, scale, n_splits, err, s);
-    if (d == 64)
-        return rd_launch<64>(q, q_stride, kc, vc, n_pages, block_table, max_pages, token_pos, token_seq, part_acc,
-                             part_ml, out, T, nh, nkv, page_size, window, scale, n_splits, err, s);
-    return ILLM_ERR_BAD_ARG;
+    RdRope rp = {partials, splits, split_stride, (const float2*)cos_sin, rot, table_positions, (bf16*)kc, (bf16*)vc,
+                 write_kv, step_err};
+    return rd_run(qkv, (nh + 2 * nkv) * d, kc, vc, n_pages, block_table, max_pages, token_pos, token_seq, part_acc,
+                  part_ml, out, T, nh, nkv, d, page_size, window, scale, n_splits, err, stream, &rp);
 }

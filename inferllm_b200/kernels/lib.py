@@ -25,6 +25,8 @@ _SIGNATURES = {
     "illm_attention_decode_supported": [I, I, I],
     "illm_attention_decode_gqa": [P, I, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
     "illm_attention_decode_ring": [P, I, P, P, LL, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P],
+    "illm_attention_decode_ring_rope": [P, P, I, LL, P, I, I, I, P, P, LL, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I,
+                                        P, P, P],
     "illm_attention_prefill": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],
     "illm_gemm_bf16_tc": [P, P, P, I, I, I, I, P, I, P, P, I],
     "illm_splitk_reduce": [P, P, I, LL, I, P],

@@ -317,28 +317,63 @@ def attention_decode_ring_splits(T, n_kv_heads, max_len) -> int:
 
 
 def attention_decode_ring(qkv, k_cache, v_cache, block_table, token_pos, token_seq, n_heads, n_kv_heads,
-                          head_dim, page_size, window, scale, max_len, splits=None):
+                          head_dim, page_size, window, scale, max_len, splits=None, rope=None):
     """bfloat16 attention of single tokens as a stream: K/V tiles of 64 keys by TMA through a ring
     of shared-memory stages, the query heads of a KV head as rows of warp-level MMAs, the tiles
     of a token dealt round-robin to `splits` blocks and merged in a fixed order.  Group sizes
-    1..16, head size 64 or 128, pages of a multiple of 64 positions."""
-    _need(qkv, "qkv", torch.bfloat16, 2)
+    1..16, head size 64 or 128, pages of a multiple of 64 positions.
+
+    `rope` = (cos_sin table or None, rot_dim, write_kv, step error word): the kernel also does what
+    `rope_kv_write` does (rotation of Q and of the new K row, K and V into the cache pages); `qkv`
+    is then the unrotated packed projection, as a bfloat16 tensor or as `SplitKPartials`."""
+    partials = None
+    if isinstance(qkv, SplitKPartials):
+        if rope is None:
+            raise KernelError("attention_decode_ring: unreduced slices need the fused position encoding")
+        partials = qkv
+        T = partials.rows
+        width = partials.cols
+    else:
+        _need(qkv, "qkv", torch.bfloat16, 2)
+        T, width = qkv.shape
     _need(k_cache, "k_cache", torch.bfloat16, 4)
     _need(v_cache, "v_cache", torch.bfloat16, 4)
-    T = qkv.shape[0]
-    out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    if rope is not None and width != (n_heads + 2 * n_kv_heads) * head_dim:
+        raise KernelError(f"qkv width {width} is not (heads + 2 kv heads) * head_dim")
+    out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=k_cache.device)
     for t0 in range(0, T, 65535):
         t1 = min(T, t0 + 65535)
         n = attention_decode_ring_splits(t1 - t0, n_kv_heads, max_len) if splits is None else int(splits)
         part_acc = part_ml = None
         if n > 1:
-            part_acc = torch.empty((t1 - t0, n_heads, n, head_dim), dtype=torch.float32, device=qkv.device)
-            part_ml = torch.empty((t1 - t0, n_heads, n, 2), dtype=torch.float32, device=qkv.device)
-        _check(load().illm_attention_decode_ring(
-            _ptr(qkv[t0:t1]), qkv.shape[1], _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table),
-            block_table.shape[1], _ptr(token_pos[t0:t1]), _ptr(token_seq[t0:t1]), _ptr(part_acc), _ptr(part_ml),
-            _ptr(out[t0:t1]), t1 - t0, n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale),
-            n, _ptr(tc_error_word(qkv.device)), _stream()), "attention_decode_ring")
+            part_acc = torch.empty((t1 - t0, n_heads, n, head_dim), dtype=torch.float32, device=out.device)
+            part_ml = torch.empty((t1 - t0, n_heads, n, 2), dtype=torch.float32, device=out.device)
+        if rope is None:
+            _check(load().illm_attention_decode_ring(
+                _ptr(qkv[t0:t1]), width, _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table),
+                block_table.shape[1], _ptr(token_pos[t0:t1]), _ptr(token_seq[t0:t1]), _ptr(part_acc), _ptr(part_ml),
+                _ptr(out[t0:t1]), t1 - t0, n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale),
+                n, _ptr(tc_error_word(out.device)), _stream()), "attention_decode_ring")
+            continue
+        table, rot_dim, write_kv, step_err = rope
+        n_pos = 0
+        if rot_dim:
+            _need(table, "cos_sin", torch.float32, 3)
+            if table.shape[1] != rot_dim // 2:
+                raise KernelError("cos_sin table does not match rot_dim")
+            n_pos = table.shape[0]
+        if T > 65535:
+            raise KernelError("attention_decode_ring with the position encoding inside takes at most 65535 tokens")
+        _check(load().illm_attention_decode_ring_rope(
+            None if partials is not None else _ptr(qkv),
+            _ptr(partials.ws) if partials is not None else None,
+            partials.splits if partials is not None else 0,
+            T * width if partials is not None else 0,
+            _ptr(table) if rot_dim else None, int(rot_dim), n_pos, 1 if write_kv else 0, _ptr(k_cache), _ptr(v_cache),
+            k_cache.shape[0], _ptr(block_table), block_table.shape[1], _ptr(token_pos[t0:t1]), _ptr(token_seq[t0:t1]),
+            _ptr(part_acc), _ptr(part_ml), _ptr(out[t0:t1]), t1 - t0, n_heads, n_kv_heads, head_dim, page_size,
+            int(window or 0), float(scale), n, _ptr(tc_error_word(out.device)), _ptr(step_err), _stream()),
+            "attention_decode_ring_rope")
     return out
 
 

@@ -63,6 +63,18 @@ class Attention(Mixer):
         return self._run(h, ctx, cache, True)
 
     def _run(self, h, ctx, cache, defer_output):
+        rotation = self.position.rotation_table()
+        if (ctx.is_decode and rotation is not None and rotation[1] % 16 == 0
+                and ops.attention_decode_ring_supported(h.dtype, self.n_heads, self.n_kv_heads, self.head_dim,
+                                                        cache.page_size)):
+            # one token per sequence: the attention kernel itself adds up the K slices of the
+            # projection, rotates Q and the new K row and writes K and V into the cache
+            qkv = ops.linear(h, self.w_qkv, defer_reduce=True)
+            o = ops.attention_decode_ring(qkv, cache.k, cache.v, cache.block_table, ctx.token_pos, ctx.token_seq,
+                                          self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size,
+                                          self.window, self.scale, ctx.max_seq_len,
+                                          rope=(rotation[0], rotation[1], cache.writes, ctx.err))
+            return ops.linear(o, self.w_o, defer_reduce=defer_output)
         # the packed projection may stay in K slices if the position encoding's kernel adds them up
         qkv = ops.linear(h, self.w_qkv, defer_reduce=self.position.takes_partials)
         geometry = (self.n_heads, self.n_kv_heads, self.head_dim)

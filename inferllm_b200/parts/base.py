@@ -99,6 +99,13 @@ class PositionEncoding(Part):
     def prepare(self) -> None:
         """Build device tables; called once after construction on a device."""
 
+    def rotation_table(self):
+        """(cos/sin table float32 [positions, rot_dim/2, 2] or None, rot_dim) if all this encoding
+        does is the rotate-half rotation of the first rot_dim channels of every Q and K head by
+        angles from that table (rot_dim 0: nothing at all), so that a mixer whose kernel can do that
+        itself may skip `encode_and_store`; None (default) for any other encoding."""
+        return None
+
     def encode_and_store(self, qkv, geometry, ctx, kv):
         """Encode positions into the Q and K heads of the packed projection `qkv` and store the
         new K and V in the cache (if `kv.writes`).  Returns the tensor that holds the encoded

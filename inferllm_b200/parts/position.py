@@ -40,6 +40,9 @@ class RopeHalf(PositionEncoding):
         table = torch.stack((torch.cos(ang), torch.sin(ang)), dim=-1).to(torch.float32)
         self.table = table.contiguous().to(self.rt.device)
 
+    def rotation_table(self):
+        return (self.table, self.rot_dim)
+
     def encode_and_store(self, qkv, geometry, ctx, kv):
         n_heads, n_kv_heads, head_dim = geometry
         return ops.rope_kv_write(qkv, self.table, self.rot_dim, ctx.token_pos, ctx.token_seq,
@@ -50,6 +53,9 @@ class RopeHalf(PositionEncoding):
 @register_position("none")
 class NoPosition(PositionEncoding):
     takes_partials = True
+
+    def rotation_table(self):
+        return (None, 0)
 
     def encode_and_store(self, qkv, geometry, ctx, kv):
         n_heads, n_kv_heads, head_dim = geometry

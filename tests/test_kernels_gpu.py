@@ -563,6 +563,59 @@ def test_attention_decode_ring(nh, nkv, d, page, window):
     assert torch.equal(cold.cpu(), out.cpu())
 
 
+@pytest.mark.parametrize("nh,nkv,d,page,window,rot,slices", [
+    (8, 2, 128, 64, None, 128, 3), (4, 4, 128, 64, None, 128, 1), (6, 2, 64, 64, 70, 64, 2), (3, 3, 64, 128, None, 32, 4),
+    (16, 1, 64, 64, None, 0, 2), (32, 8, 128, 64, None, 128, 0)])
+def test_attention_decode_ring_with_the_position_encoding_inside(nh, nkv, d, page, window, rot, slices):
+    """The kernel that also rotates Q and the new K row and writes K and V into the cache, fed with
+    the unrotated projection (bfloat16, or K slices of a split product), against the two kernels
+    it replaces: the same attention output and the same cache contents, for every number of splits
+    (the new row lies in another block's tile each time)."""
+    lens = [1, 63, 64, 65, 700, 1024, 3, 129]
+    T = len(lens)
+    pc = Paged(lens, nkv, d, page, torch.bfloat16, seed=d + nh)
+    g = torch.Generator().manual_seed(11)
+    width = (nh + 2 * nkv) * d
+    if slices:
+        ws = torch.randn(slices, T, width, generator=g) * (1.0 / math.sqrt(slices))
+        part = ops.SplitKPartials(dev(ws))
+        qkv_bf16 = part.materialize(torch.bfloat16)
+    else:
+        qkv_bf16 = dev(torch.randn(T, width, generator=g).bfloat16())
+    seq, pos = dev(torch.arange(T, dtype=torch.int32)), dev(torch.tensor([n - 1 for n in lens], dtype=torch.int32))
+    scale = 1.0 / math.sqrt(d)
+    table = None
+    if rot:
+        from inferllm_b200.config import PartSpec
+        from inferllm_b200.parts import Runtime, build_part
+        rope = build_part("position", PartSpec("rope_half", dict(head_dim=d, rot_dim=rot, theta=1e4, max_positions=2048)),
+                          Runtime(torch.device("cuda"), torch.bfloat16))
+        rope.prepare()
+        table = rope.table
+    # the two kernels: rotation and cache write (from the slices, as the engine would), then attention
+    kc1, vc1 = dev(pc.kc), dev(pc.vc)
+    src = ops.SplitKPartials(part.ws.clone()) if slices else qkv_bf16.clone()
+    q1 = ops.rope_kv_write(src, table, rot, pos, seq, dev(pc.table), kc1, vc1, nh, nkv, d, page, True, err_word())
+    want = ops.attention_decode_ring(q1, kc1, vc1, dev(pc.table), pos, seq, nh, nkv, d, page, window, scale, 4096)
+    assert np.isfinite(f64(want)).all()
+    for splits in (None, 1, 2, 5, 16):
+        kc2, vc2 = dev(pc.kc), dev(pc.vc)
+        e = err_word()
+        got = ops.attention_decode_ring(part if slices else qkv_bf16, kc2, vc2, dev(pc.table), pos, seq, nh, nkv, d, page,
+                                        window, scale, 4096, splits=splits, rope=(table, rot, True, e))
+        assert int(e.item()) == 0 and int(ops.tc_error_word(torch.device("cuda")).item()) == 0
+        for b in range(T):
+            pg, off = int(pc.table[b, (lens[b] - 1) // page]), (lens[b] - 1) % page
+            assert torch.equal(kc2[pg, :, off], kc1[pg, :, off]) and torch.equal(vc2[pg, :, off], vc1[pg, :, off]), \
+                f"cache row of sequence {b}, {splits} splits"
+        assert maxrel(f64(got), f64(want)) <= 2 ** -9, f"{splits} splits"
+    # a layer that reads another layer's cache entry: nothing is written
+    kc3, vc3 = kc1.clone(), vc1.clone()
+    got = ops.attention_decode_ring(part if slices else qkv_bf16, kc3, vc3, dev(pc.table), pos, seq, nh, nkv, d, page,
+                                    window, scale, 4096, rope=(table, rot, False, err_word()))
+    assert torch.equal(kc3.view(torch.int16), kc1.view(torch.int16)) and maxrel(f64(got), f64(want)) <= 2 ** -9
+
+
 def test_attention_decode_says_what_it_takes():
     assert not ops.attention_decode_supported(torch.float32, 4, 4, 128, 64)
     assert not ops.attention_decode_supported(torch.bfloat16, 4, 4, 24, 64)
