@@ -90,9 +90,30 @@ __device__ __forceinline__ void rd_encoded_chunk(const RdRope& rp, const bf16* _
         if (rp.partials) {
 #pragma unroll
             for (int k = 0; k < 8; k++) o8[k] = 0.f;
-            for (int z = 0; z < rp.splits; z++) {
+            const float* pz = rp.partials + off;
+            int z = 0;
+            for (; z + 4 <= rp.splits; z += 4) {          // four slices in flight, added in order
+                float p8[4][8];
+#pragma unroll
+                for (int u = 0; u < 4; u++) load8(pz + (size_t)(z + u) * rp.split_stride, p8[u]);
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+#pragma unroll
+                    for (int k = 0; k < 8; k++) o8[k] += p8[u][k];
+            }
+            if (z + 2 <= rp.splits) {
+                float p8[2][8];
+                load8(pz + (size_t)z * rp.split_stride, p8[0]);
+                load8(pz + (size_t)(z + 1) * rp.split_stride, p8[1]);
+#pragma unroll
+                for (int k = 0; k < 8; k++) o8[k] += p8[0][k];
+#pragma unroll
+                for (int k = 0; k < 8; k++) o8[k] += p8[1][k];
+                z += 2;
+            }
+            if (z < rp.splits) {
                 float p8[8];
-                load8(rp.partials + (size_t)z * rp.split_stride + off, p8);
+                load8(pz + (size_t)z * rp.split_stride, p8);
 #pragma unroll
                 for (int k = 0; k < 8; k++) o8[k] += p8[k];
             }
