@@ -74,6 +74,22 @@ class Sampler:
         self.params = params
         self._window = None          # int32 [requests of the batch, repeat_last_n] on the device
         self._row_of = {}            # request -> its row of the window
+        self._u_ring, self._u_next = [None] * 4, 0     # pinned staging for the uniform numbers
+
+    def _uniforms(self, requests, steps, device):
+        """The step's uniform numbers on the device, through pinned memory and a copy that does not
+        make the host wait for the work already queued (a copy from pageable memory would)."""
+        n = len(requests)
+        slot = self._u_next
+        self._u_next = (slot + 1) % len(self._u_ring)
+        buf = self._u_ring[slot]
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 64), dtype=torch.float32, pin_memory=(device.type == "cuda"))
+            self._u_ring[slot] = buf
+        view = buf.numpy()
+        for i, (r, st) in enumerate(zip(requests, steps)):
+            view[i] = uniform_for(self.params.seed, r, st)
+        return buf[:n].to(device, non_blocking=True)
 
     def _wants_history(self) -> bool:
         return self.params.repeat_penalty != 1.0 and self.params.repeat_last_n > 0
@@ -116,8 +132,7 @@ class Sampler:
             u = torch.zeros(B, dtype=torch.float32, device=logits.device)
             toks = ops.sample(logits, u, 1.0, 1, 1.0, p.repeat_penalty, last)
         else:
-            u = torch.tensor([uniform_for(p.seed, r, s) for r, s in zip(requests, steps)],
-                             dtype=torch.float32).to(logits.device)
+            u = self._uniforms(requests, steps, logits.device)
             toks = ops.sample(logits, u, p.temp, p.top_k, p.top_p, p.repeat_penalty, last)
         if self._wants_history() and self._window is not None and (on_device or histories is not None) \
                 and all(r in self._row_of for r in requests):
