@@ -1,7 +1,8 @@
 // Causal attention of whole prompts over the paged cache on the 5th-generation tensor cores.
 //
-// One block owns a tile of 128 consecutive query tokens of one (sequence, head); two blocks share
-// an SM.  Four softmax warps: a thread owns one query row, which is also one lane of tensor memory.
+// One block owns two tiles of 128 consecutive query tokens of one (sequence, head), the x-th from
+// the end of the prompt and the x-th from its start, which under the causal mask gives every block of
+// a prompt the same number of key blocks; it does them one after the other.  Two blocks share an SM.  Four softmax warps: a thread owns one query row, which is also one lane of tensor memory.
 // Keys and values come in blocks of 64 straight from the cache pages by TMA (128-byte swizzle), K
 // through a ring of three stages and V through a ring of two.  Tensor memory of a block, 256
 // columns: two score buffers S0, S1 of 64 columns and the output accumulator O of `head size`.
@@ -177,24 +178,32 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        bar_init(q_full, 1);
+    auto init_barriers = [&](bool again) {
+        // `again`: the barriers have been used for a tile and are quiet (every load has landed, every
+        // commit has arrived, nobody waits); they are invalidated and made anew, so that the next
+        // tile starts with every phase at zero
+        auto one = [&](unsigned bar, unsigned count) {
+            if (again) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+            bar_init(bar, count);
+        };
+        one(q_full, 1);
         for (int i = 0; i < FT_KSTAGES; i++) {
-            bar_init(k_full0 + 8 * i, 1);
-            bar_init(k_empty0 + 8 * i, 1);
+            one(k_full0 + 8 * i, 1);
+            one(k_empty0 + 8 * i, 1);
         }
         for (int i = 0; i < FT_VSTAGES; i++) {
-            bar_init(v_full0 + 8 * i, 1);
-            bar_init(v_empty0 + 8 * i, 1);
+            one(v_full0 + 8 * i, 1);
+            one(v_empty0 + 8 * i, 1);
         }
-        bar_init(s_full0, 1);
-        bar_init(s_full0 + 8, 1);
-        bar_init(p_full0, FT_BM);          // one per score buffer: a fast warp may be a block ahead of a slow one
-        bar_init(p_full0 + 8, FT_BM);
-        bar_init(pv_done, 1);
+        one(s_full0, 1);
+        one(s_full0 + 8, 1);
+        one(p_full0, FT_BM);               // one per score buffer: a fast warp may be a block ahead of a slow one
+        one(p_full0 + 8, FT_BM);
+        one(pv_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
+    };
+    if (threadIdx.x == 0) init_barriers(false);
     if (warp == FT_MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(s_u32(tmem_holder_p)), "r"(TMEM_COLS) : "memory");
@@ -206,9 +215,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const unsigned tmem = *tmem_holder_p;
     pdl_grid_sync();
 
-    // ---- which rows and keys.  The last tiles of a prompt see the most keys and start first.
-    const int b = blockIdx.z, h = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
+    // ---- which rows and keys.  A block owns two tiles of its sequence, the x-th from the end and the
+    // x-th from the start: with a causal mask their key blocks add up to the same number for every
+    // x, so all blocks of a prompt have equal work.  The two are done one after the other, the
+    // second on freshly made barriers.
+    const int b = blockIdx.z, h = blockIdx.y;
     const int q0 = cu_q[b], qlen = cu_q[b + 1] - q0;
+    const int n_tiles = (qlen + FT_BM - 1) / FT_BM;
+    for (int part = 0; part < 2; part++) {
+    const int tile = part == 0 ? n_tiles - 1 - (int)blockIdx.x : (int)blockIdx.x;
+    if (part == 0 ? tile < (int)blockIdx.x : tile >= n_tiles - 1 - (int)blockIdx.x) continue;   // uniform over the block
+    if (part == 1) {
+        fence_before();
+        __syncthreads();
+        if (threadIdx.x == 0) init_barriers(true);
+        __syncthreads();
+        fence_after();
+    }
     const int row0 = tile * FT_BM;
     const int total = seq_lens[b], past = total - qlen;
     const int hk = h / (nh / nkv);
@@ -416,6 +439,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
         }
     }
+    }   // the block's two tiles
     fence_before();
     __syncthreads();
     if (warp == FT_MMA_WARP) {
@@ -471,7 +495,7 @@ static int ft_launch(const void* q, int q_stride, int T, const void* kc, const v
     auto kern = attention_prefill_tc_kernel<D>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    dim3 grid((max_q + FT_BM - 1) / FT_BM, nh, B);
+    dim3 grid(((max_q + FT_BM - 1) / FT_BM + 1) / 2, nh, B);     // two tiles per block
     illm_launch(kern, grid, dim3(FT_THREADS), smem, s, mq, mk, mv, block_table, max_pages, cu_q, seq_lens,
                 (bf16*)out, nh, nkv, page_size, window, scale * 1.4426950408889634f, err);
     return illm_launch_status();
