@@ -226,7 +226,9 @@ static int pick_stages(int stage_bytes, long long n_blocks, int k_iters_per_bloc
     if (g_tc_stages_override > 0) return g_tc_stages_override;
     const int per_sm = (int)((n_blocks + 147) / 148);
     const int resident = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
-    int stages = (216 * 1024 / resident - 2048) / stage_bytes;
+    // an SM has 227 KB; a block costs its ring, 1 KB of alignment slack, 1 KB that the system keeps
+    // and its few static bytes
+    int stages = (227 * 1024 / resident - 2560) / stage_bytes;
     if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
     if (stages > k_iters_per_block) stages = k_iters_per_block;
     return stages < 2 ? 2 : stages;
