@@ -222,7 +222,10 @@ def main():
 
     # one engine for every scenario: cache for the batch at full context, or 64 short sequences
     decode_room = K + W + 8
-    max_tokens = max(B * CONTEXT, 64 * (-(-(512 + decode_room) // 64) * 64), PREFILL_TOKENS) + 64
+    if args.only == "decode":           # one scenario: room for the batch at the context asked for
+        max_tokens = B * (-(-(args.context + 8) // 64) * 64) + 64
+    else:
+        max_tokens = max(B * CONTEXT, 64 * (-(-(512 + decode_room) // 64) * 64), PREFILL_TOKENS) + 64
     model = Model(ModelConfig(compt_type="bfloat16", nr_ctx=CONTEXT, max_tokens=max_tokens, max_batch=max(B, 64)))
     model.load_random(cfg, seed=0)
     ops.set_gemm_backend(args.gemm)

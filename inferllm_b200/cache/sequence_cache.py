@@ -126,8 +126,23 @@ class SequenceCache:
             g.entries.append(entry)
         self.runtime = runtime
         if runtime is not None:
+            self._check_fits(runtime)
             for g in self.paged + self.states:
                 g.allocate(runtime)
+
+    def _check_fits(self, runtime) -> None:
+        """Refuse a cache that the device cannot hold, in words, before any allocation."""
+        import torch
+        if runtime.device.type != "cuda":
+            return
+        elem = torch.empty((), dtype=runtime.dtype).element_size()
+        need = sum(g.bytes(elem) for g in self.paged)
+        free, _ = torch.cuda.mem_get_info(runtime.device)
+        free += torch.cuda.memory_reserved(runtime.device) - torch.cuda.memory_allocated(runtime.device)
+        if need > free:
+            tokens = max((g.ledger.pool.n * g.ledger.page_size for g in self.paged), default=0)
+            raise CacheError(f"a cache for {tokens} tokens needs {need / 2**30:.1f} GiB, the device has "
+                             f"{free / 2**30:.1f} GiB free: ask for fewer tokens (max_tokens)")
 
     # ---- slots
 
