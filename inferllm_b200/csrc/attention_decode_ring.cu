@@ -18,6 +18,13 @@
 // ascending order of the split.  The result never depends on timing.
 // Keys outside [p - window + 1, p] get weight exactly 0 and their V rows are cleared in shared
 // memory before the product (a page may still hold another sequence's values there).
+// In its second form (FUSE, illm_attention_decode_ring_rope) the kernel also does the position
+// encoding and the cache write of the step (what rope_kv.cu does, src/kern/naive/naive.cpp:389-414
+// and src/core/op.cpp:414-416 in the reference): the consumer warps rotate the query heads on
+// their way into shared memory, and in the block that owns the token's last tile a sixth warp makes
+// the token's new K row (rotated) and V row, writes them to the cache page and hands them through
+// shared memory to the consumer warp that owns their place in that tile.  The TMA thread starts
+// at once: it needs neither.
 // Formulas: src/kern/naive/naive.cpp:576-604 (scores with key head h / G), :531-553 (mask),
 // :209-240 (softmax), :634-662 (values); the reference's GPU code loops over the heads with one
 // library call each (src/kern/gpu/kernel_gpu.cu:688-756).
