@@ -178,7 +178,13 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();          // the barriers exist; from here the warps go their own ways
-    pdl_grid_sync();
+    // Programmatic dependent launch.  What the step's sequences hold (positions, page tables) and
+    // the K and V of earlier positions were written before this step began, so in the fused form
+    // the TMA thread does not wait for the previous kernel (the Q/K/V product): its first tiles are
+    // on their way while that kernel drains.  Everything that reads the projection or writes global
+    // memory waits.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!FUSE) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int split = blockIdx.x, hk = blockIdx.y, t = blockIdx.z;
     const int p = token_pos[t];
@@ -188,6 +194,7 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
     const int n_my = split < n_tiles ? (n_tiles - split + n_splits - 1) / n_splits : 0;
     if (n_my == 0) {
         // no keys for this split: the merge kernel skips partials whose maximum is -inf
+        if (FUSE) asm volatile("griddepcontrol.wait;" ::: "memory");
         if (tid < G) {
             const size_t o = ((size_t)t * nh + hk * G + tid) * n_splits + split;
             part_ml[o * 2] = -INFINITY;
@@ -209,6 +216,7 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
         // lanes a chunk of the V row; they go to the cache page and to shared memory, from where the
         // consumer warp that owns the row's place in the last tile takes them
         if (new_row_here) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             if (lane < 2 * CH) {
                 const bool is_k = lane < CH;
                 const int c = is_k ? lane : lane - CH;
@@ -265,6 +273,7 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
     }
 
     // ---- consumers.  Q: the G heads of this kv head as rows 0..G-1, zero rows above
+    if (FUSE) asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int i = tid; i < 16 * CH; i += RD_CONSUMERS * 32) {
         const int r = i / CH, c = i % CH;
         if (FUSE && r < G) {

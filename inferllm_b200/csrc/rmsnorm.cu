@@ -50,7 +50,15 @@ __global__ void __launch_bounds__(RN_MAX_THREADS)
 add_rmsnorm_reg_kernel(float* __restrict__ resid, const TA* __restrict__ delta, const TW* __restrict__ w,
                        TA* __restrict__ y, const int* __restrict__ rows, int H, float eps, int write_resid,
                        const float* __restrict__ partials, int splits, long long split_stride) {
-    pdl_grid_sync();
+    // the norm's weight is no result of the previous kernel: it is read while that kernel drains
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    float wv[ITERS][8];
+#pragma unroll
+    for (int i = 0; i < ITERS; i++) {
+        const int c = (threadIdx.x + i * (int)blockDim.x) * 8;
+        if (c < H) load8(w + c, wv[i]);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ float scratch[32];
     const int r = rows ? rows[blockIdx.x] : blockIdx.x;
     float* x = resid + (size_t)r * H;
@@ -104,10 +112,9 @@ add_rmsnorm_reg_kernel(float* __restrict__ resid, const TA* __restrict__ delta, 
     for (int i = 0; i < ITERS; i++) {
         const int c = (threadIdx.x + i * (int)blockDim.x) * 8;
         if (c < H) {
-            float w8[8], r8[8];
-            load8(w + c, w8);
+            float r8[8];
 #pragma unroll
-            for (int k = 0; k < 8; k++) r8[k] = (v[i][k] * scale) * w8[k];
+            for (int k = 0; k < 8; k++) r8[k] = (v[i][k] * scale) * wv[i][k];
             store8(o + c, r8);
         }
     }
