@@ -266,3 +266,29 @@ def test_layers_of_real_width_bfloat16_against_float32():
     assert_close(t16, w32, "bfloat16", "last 32 one by one, real widths")
     for r in range(3):
         assert_close(b16[r], b32[r], "bfloat16", f"request {r} in a batch, real widths")
+
+
+def test_random_batches_against_float32():
+    """Forty batches of random size (1..12), random prompt lengths (2..3000), random numbers of
+    single-token steps and sequences that end at different times, on a mid-sized model with grouped
+    heads: one request of every batch is replayed alone on the float32 engine and must agree; the
+    kernels' error words stay clear and the cache keeps its invariants."""
+    from inferllm_b200 import Engine, EngineOptions, config_from_dict
+    cfg = config_from_dict(dict(architectures=["LlamaForCausalLM"], hidden_size=1024, num_hidden_layers=3,
+                                num_attention_heads=8, num_key_value_heads=2, head_dim=128, intermediate_size=2816,
+                                vocab_size=5000, max_position_embeddings=4096))
+    eng = Engine.from_config(cfg, EngineOptions(dtype="bfloat16", max_tokens=40000, max_batch=12), 5)
+    ref = Engine.from_config(cfg, EngineOptions(dtype="float32", max_tokens=8192, max_batch=2), 5)
+    rng = np.random.default_rng(1)
+    for _ in range(40):
+        B = int(rng.integers(1, 13))
+        lens = [int(rng.integers(2, 3000)) for _ in range(B)]
+        n_dec = int(rng.integers(1, 40))
+        pre = [max(1, n - int(rng.integers(0, n_dec + 1))) for n in lens]
+        reqs = [rng.integers(0, 5000, size=n).tolist() for n in lens]
+        i = int(rng.integers(0, B))
+        got = in_batches(eng, reqs, pre, [list(range(B))])[i]
+        want = in_batches(ref, [reqs[i]], [pre[i]], [[0]])[0]
+        assert_close(got[pre[i] - 1:], want[pre[i] - 1:], "bfloat16", f"request {i} of a batch of {B} (lengths {lens})")
+        eng.check_device_errors()
+        eng.cache.check()
