@@ -45,8 +45,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restri
 // has one thread per 8 elements up to 1024 threads (a function of H alone: the order of the sums,
 // and with it every bit of the result, is the same for one row and for thousands).
 #define RN_MAX_THREADS 1024
-template <typename TA, typename TW, int ITERS>
-__global__ void __launch_bounds__(RN_MAX_THREADS)
+template <typename TA, typename TW, int ITERS, int MAXT>
+__global__ void __launch_bounds__(MAXT)
 add_rmsnorm_reg_kernel(float* __restrict__ resid, const TA* __restrict__ delta, const TW* __restrict__ w,
                        TA* __restrict__ y, const int* __restrict__ rows, int H, float eps, int write_resid,
                        const float* __restrict__ partials, int splits, long long split_stride) {
@@ -82,7 +82,17 @@ add_rmsnorm_reg_kernel(float* __restrict__ resid, const TA* __restrict__ delta, 
                 float d8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                 const float* pz = partials + (size_t)r * H + c;
                 int z = 0;
-                for (; z + 4 <= splits; z += 4) {        // four slices in flight, added in order
+                constexpr int FLY = MAXT <= 512 ? 8 : 4;   // slices in flight (registers allowing), added in order
+                for (; z + FLY <= splits; z += FLY) {
+                    float p8[FLY][8];
+#pragma unroll
+                    for (int q = 0; q < FLY; q++) load8(pz + (size_t)(z + q) * split_stride, p8[q]);
+#pragma unroll
+                    for (int q = 0; q < FLY; q++)
+#pragma unroll
+                        for (int k = 0; k < 8; k++) d8[k] += p8[q][k];
+                }
+                if (FLY == 8 && z + 4 <= splits) {
                     float p8[4][8];
 #pragma unroll
                     for (int q = 0; q < 4; q++) load8(pz + (size_t)(z + q) * split_stride, p8[q]);
@@ -90,6 +100,7 @@ add_rmsnorm_reg_kernel(float* __restrict__ resid, const TA* __restrict__ delta, 
                     for (int q = 0; q < 4; q++)
 #pragma unroll
                         for (int k = 0; k < 8; k++) d8[k] += p8[q][k];
+                    z += 4;
                 }
                 for (; z < splits; z++) {
                     float p8[8];
@@ -131,11 +142,12 @@ static int launch(float* resid, const void* delta, const void* w, void* y, const
         if (threads > RN_MAX_THREADS) threads = RN_MAX_THREADS;
         if (threads < 64) threads = 64;
         const int iters = (chunks + threads - 1) / threads;
-#define RN_CASE(N)                                                                                   \
-    illm_launch(add_rmsnorm_reg_kernel<TA, TW, N>, dim3(n_rows), dim3(threads), 0, s, resid, (const TA*)delta, (const TW*)w, \
+#define RN_CASE(N, MT)                                                                               \
+    illm_launch(add_rmsnorm_reg_kernel<TA, TW, N, MT>, dim3(n_rows), dim3(threads), 0, s, resid, (const TA*)delta, (const TW*)w, \
                                                                    (TA*)y, rows, H, eps, write_resid, partials, splits, split_stride)
-        if (iters <= 1) RN_CASE(1);
-        else RN_CASE(2);
+        if (iters <= 1 && threads <= 512) RN_CASE(1, 512);
+        else if (iters <= 1) RN_CASE(1, RN_MAX_THREADS);
+        else RN_CASE(2, RN_MAX_THREADS);
 #undef RN_CASE
         return illm_launch_status();
     }

@@ -512,7 +512,7 @@ def gemm_tc_splits(M, N, K):
         return 1
     tiles = -(-N // 128)
     k_iters = -(-K // 64)
-    splits = max(1, min(2 * N_SMS // tiles, k_iters // 8))
+    splits = max(1, min(2 * N_SMS // tiles, k_iters // 8, 8))     # (more than 8 slices cost their readers more than they win)
     per = -(-k_iters // splits)
     return -(-k_iters // per)          # every slice owns at least one 64-wide piece of K
 
