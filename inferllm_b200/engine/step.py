@@ -36,7 +36,9 @@ class EngineError(RuntimeError):
 class EngineOptions:
     dtype: str = "bfloat16"        # "bfloat16": serving kernels; "float32": everything in true 32-bit
     device_id: int = 0
-    max_tokens: int = 4096         # tokens that live sequences may hold together (sizes the cache)
+    max_tokens: Optional[int] = 4096    # tokens that live sequences may hold together (sizes the cache);
+                                        # None: what `mem_fraction` of the memory left beside the weights holds
+    mem_fraction: float = 0.9
     max_seq_len: Optional[int] = None   # longest sequence; default the model's max positions
     max_batch: Optional[int] = None     # slots; default max_tokens / page_size
     page_size: int = 64
@@ -132,7 +134,10 @@ class Engine:
         self.vocab_size = spec.vocab_size
         max_seq = min(options.max_seq_len or spec.max_positions, spec.max_positions)
         ps = options.page_size
-        num_pages = max(1, -(-options.max_tokens // ps))
+        max_tokens = options.max_tokens
+        if max_tokens is None:
+            max_tokens = self._tokens_that_fit(options.mem_fraction)
+        num_pages = max(1, -(-max_tokens // ps))
         num_slots = options.max_batch or num_pages
         self.cache = SequenceCache(self.model.cache_requests(), num_slots, num_pages, ps, max_seq,
                                    self.rt)
@@ -143,6 +148,28 @@ class Engine:
         self._graphs = {}
         self._graph_pool = None
         self.loaded = False
+
+    def _tokens_that_fit(self, fraction: float) -> int:
+        """How many tokens of cache fit into `fraction` of the device memory that is free now and not
+        needed for the weights (which are loaded after the cache is made)."""
+        from ..parts.base import PagedKV
+        elem = 4 if self.rt.is_f32 else 2
+        weights = 0
+        for decl in self.model.tensor_decls().values():
+            n = 1
+            for d in decl.shape:
+                n *= int(d)
+            weights += n * elem
+        per_token = sum(2 * r.n_kv_heads * r.head_dim * elem for r in self.model.cache_requests().values()
+                        if isinstance(r, PagedKV))
+        free, _ = torch.cuda.mem_get_info(self.rt.device)
+        room = int((free - weights) * fraction)
+        if per_token == 0:
+            return self.options.page_size
+        if room < per_token * self.options.page_size:
+            raise EngineError(f"the weights ({weights / 2**30:.1f} GiB) leave no room for a cache on this device "
+                              f"({free / 2**30:.1f} GiB free)")
+        return room // per_token
 
     def _make_runtime(self, options: EngineOptions) -> Runtime:
         if not torch.cuda.is_available():

@@ -292,3 +292,22 @@ def test_random_batches_against_float32():
         assert_close(got[pre[i] - 1:], want[pre[i] - 1:], "bfloat16", f"request {i} of a batch of {B} (lengths {lens})")
         eng.check_device_errors()
         eng.cache.check()
+
+
+def test_cache_sized_from_the_memory_that_is_left(model_folders):
+    """max_tokens=None: the cache takes `mem_fraction` of what the device has free beside the weights."""
+    import gc
+
+    from inferllm_b200 import Engine, EngineOptions
+    gc.collect()
+    torch.cuda.empty_cache()
+    free, total = torch.cuda.mem_get_info()
+    eng = Engine.from_folder(model_folders["A"], EngineOptions(dtype="bfloat16", max_tokens=None, mem_fraction=0.05,
+                                                               max_batch=4, page_size=64))
+    cfg = TINY["A"]
+    per_token = 2 * cfg["num_hidden_layers"] * cfg.get("num_key_value_heads", cfg["num_attention_heads"]) \
+        * (cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"]) * 2
+    held = eng.cache.pages_free()[0] * 64 * per_token
+    assert 0.03 * free <= held <= 0.05 * total
+    ids = random_prompt("A", 40, 1)
+    assert whole(eng, ids).shape[0] == 40
