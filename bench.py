@@ -130,6 +130,133 @@ def prefill_flops(cfg, n_layers, T, fig):
 SCENARIOS = {"8b": "16:64:2048:256", "13b": "32:128:1024:256", "7b": "8:512:512:256"}
 
 
+def run_kernels(pk, pk_src):
+    """The hot kernels one by one at several sizes (beside the contract): each is replayed from a
+    CUDA graph of several launches on different buffers (so that nothing is served from L2 by the
+    launch before), timed with events, and printed as one JSON line with its algorithmic bytes or
+    flops against the peaks."""
+    import math
+
+    import torch
+
+    from inferllm_b200.kernels import ops
+
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+
+    def graph_us(fns, reps=10):
+        for f in fns:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for f in fns:
+                f()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps / len(fns) * 1e3
+
+    def emit(kernel, size, us, nbytes=None, flops=None):
+        line = {"kernel": kernel, "size": size, "us": round(us, 1)}
+        if nbytes is not None:
+            line["GB_per_s"] = round(nbytes / us / 1e3, 0)
+            line["frac_of_hbm"] = round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)
+        if flops is not None:
+            line["TF_per_s"] = round(flops / us / 1e6, 0)
+            line["frac_of_bf16"] = round(flops / us / 1e6 / pk["bf16_tflops"], 3)
+        line["peaks"] = pk_src
+        print(json.dumps(line), flush=True)
+
+    d, page = 128, 64
+    # ---- decode attention (the position encoding and the cache write inside)
+    for B, nh, nkv, ctx in ((1, 32, 32, 512), (1, 32, 32, 4096), (8, 32, 32, 512), (8, 32, 32, 4096), (64, 32, 32, 512),
+                            (64, 32, 32, 4096), (8, 32, 8, 4096), (1, 32, 8, 32768), (16, 32, 8, 16384), (8, 40, 40, 4096)):
+        per = -(-ctx // page)
+        n_l = max(2, min(8, int(2e9 // (B * per * page * nkv * d * 4)) or 2))
+        kc = torch.randn(n_l, B * per, nkv, page, d, device=dev).bfloat16()
+        vc = torch.randn_like(kc)
+        table = torch.arange(B * per, dtype=torch.int32, device=dev).view(B, per)
+        pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+        seq = torch.arange(B, dtype=torch.int32, device=dev)
+        qkv = torch.randn(B, (nh + 2 * nkv) * d, device=dev).bfloat16()
+        cs = torch.randn(ctx, d // 2, 2, device=dev)
+        err = torch.zeros(1, dtype=torch.int32, device=dev)
+        us = graph_us([lambda i=i: ops.attention_decode_ring(qkv, kc[i], vc[i], table, pos, seq, nh, nkv, d, page, None,
+                                                             0.088, ctx, rope=(cs, d, True, err)) for i in range(n_l)])
+        emit("attention_decode_ring (fused)", f"batch {B}, {nh} heads over {nkv}, context {ctx}", us,
+             nbytes=B * ctx * nkv * d * 4)
+        del kc, vc
+    # ---- decode-sized products (weights of the three model sizes)
+    shapes = {"7B qkv": (12288, 4096), "7B o": (4096, 4096), "7B gate/up+act": (22016, 4096), "7B down": (4096, 11008),
+              "7B head": (32000, 4096), "8B qkv": (6144, 4096), "8B gate/up+act": (28672, 4096), "8B down": (4096, 14336),
+              "8B head": (128256, 4096), "13B qkv": (15360, 5120), "13B gate/up+act": (27648, 5120), "13B down": (5120, 13824)}
+    for name, (N, K) in shapes.items():
+        n_w = max(2, min(6, int(1.5e9 // (N * K * 2))))
+        ws = [(torch.randn(N, K, device=dev) * 0.02).bfloat16() for _ in range(n_w)]
+        for M in (1, 8, 16):
+            x = torch.randn(M, K, device=dev).bfloat16()
+            if "act" in name:
+                us = graph_us([lambda w=w: ops.linear_gated(x, w) for w in ws])
+            else:
+                us = graph_us([lambda w=w: ops.linear(x, w, defer_reduce=True) for w in ws])
+            emit("gemm_tc (decode)", f"{name}, {M} tokens", us, nbytes=N * K * 2)
+        del ws
+    # ---- prompt attention
+    for T, nh, nkv in ((512, 32, 32), (2048, 32, 32), (8192, 32, 32), (16384, 32, 32), (2048, 32, 8), (16384, 32, 8)):
+        n_pages = T // page
+        kc = torch.randn(n_pages, nkv, page, d, device=dev).bfloat16()
+        vc = torch.randn_like(kc)
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, -1)
+        qkv = torch.randn(T, (nh + 2 * nkv) * d, device=dev).bfloat16()
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        sl = torch.tensor([T], dtype=torch.int32, device=dev)
+        us = graph_us([lambda: ops.attention_prefill_tc(qkv, kc, vc, table, cu, sl, T, nh, nkv, d, page, None, 0.088)] * 3)
+        emit("attention_prefill_tc", f"prompt of {T}, {nh} heads over {nkv}", us, flops=4 * nh * d * T * (T + 1) / 2)
+        del kc, vc, qkv
+    # ---- prompt-sized products on the SM-pair kernel, and the library beside them
+    x = torch.randn(2048, 4096, device=dev).bfloat16()
+    for name, (N, K) in (("7B qkv", (12288, 4096)), ("7B gate/up+act", (22016, 4096)), ("7B down", (4096, 11008))):
+        xx = x if K == 4096 else torch.randn(2048, K, device=dev).bfloat16()
+        ws = [(torch.randn(N, K, device=dev) * 0.02).bfloat16() for _ in range(3)]
+        gated = "act" in name
+        us = graph_us([lambda w=w: ops.gemm_bf16_tc2(xx, w, torch.bfloat16, gated=gated) for w in ws])
+        emit("gemm_tc2", f"{name}, 2048 tokens", us, flops=2 * 2048 * N * K)
+        if gated:
+            us = graph_us([lambda w=w: ops.swiglu(torch.mm(xx, w.t())) for w in ws])
+        else:
+            us = graph_us([lambda w=w: torch.mm(xx, w.t()) for w in ws])
+        emit("library (cuBLAS)" + (" + swiglu" if gated else ""), f"{name}, 2048 tokens", us, flops=2 * 2048 * N * K)
+        del ws
+    # ---- the memory-bound kernels of a prompt step (2,048 tokens of a 7B layer)
+    T, H, I, nh, nkv = 2048, 4096, 11008, 32, 32
+    resid = [torch.randn(T, H, device=dev) for _ in range(4)]
+    delta = [torch.randn(T, H, device=dev).bfloat16() for _ in range(4)]
+    wn = torch.ones(H, device=dev).bfloat16()
+    us = graph_us([lambda i=i: ops.add_rmsnorm(resid[i], delta[i], wn, 1e-5, torch.bfloat16) for i in range(4)])
+    emit("add_rmsnorm", "2048 tokens x 4096", us, nbytes=T * H * 12)
+    qs = [torch.randn(T, (nh + 2 * nkv) * d, device=dev).bfloat16() for _ in range(4)]
+    kcs = [torch.zeros(T // page, nkv, page, d, device=dev, dtype=torch.bfloat16) for _ in range(4)]
+    vcs = [torch.zeros_like(k) for k in kcs]
+    cs = torch.randn(4096, d // 2, 2, device=dev)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    seq = torch.zeros(T, dtype=torch.int32, device=dev)
+    table = torch.arange(T // page, dtype=torch.int32, device=dev).view(1, -1)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    us = graph_us([lambda i=i: ops.rope_kv_write(qs[i], cs, d, pos, seq, table, kcs[i], vcs[i], nh, nkv, d, page, True, err)
+                   for i in range(4)])
+    emit("rope_kv_write", "2048 tokens, 32 + 2 x 32 heads of 128", us, nbytes=T * (nh + 2 * nkv) * d * 4)
+    gu = [torch.randn(T, 2 * I, device=dev).bfloat16() for _ in range(4)]
+    us = graph_us([lambda i=i: ops.swiglu(gu[i]) for i in range(4)])
+    emit("swiglu", "2048 tokens x 11008", us, nbytes=T * I * 6)
+    return 0
+
+
 def run_scenario(args, cfg, cfgd, model_name, L, fig, pk, pk_src):
     """An unequal batch through `Model.generate`: one prompt step, then one token per sequence and
     step, host token ids in and out.  Prints one JSON line with prompt and decode tokens per second
@@ -185,6 +312,8 @@ def main():
     ap.add_argument("--gemm", default="auto", choices=["auto", "tc", "library"])
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels without programmatic dependent launch")
     ap.add_argument("--context", type=int, default=CONTEXT, help="position at which the timed decode steps end")
+    ap.add_argument("--kernels", action="store_true", help="beside the contract: the hot kernels one by one at "
+                    "several sizes, one JSON line each")
     ap.add_argument("--scenario", metavar="B:MIN:MAX:NEW", help="beside the contract: B prompts of random ids with "
                     "lengths uniform in [MIN, MAX] (seeded) prefilled in one step of unequal lengths, then NEW tokens "
                     "each, through the Python entry point; 'config' = the workload BASELINE.json names for --model "
@@ -217,6 +346,8 @@ def main():
     pk, pk_src = peaks()
     B = args.batch
 
+    if args.kernels:
+        return run_kernels(pk, pk_src)
     if args.scenario:
         return run_scenario(args, cfg, cfgd, model_name, L, fig, pk, pk_src)
 

@@ -37,7 +37,7 @@
 #define RD_BN 64                        // keys per tile
 #define RD_CONSUMERS 4
 #define RD_THREADS ((RD_CONSUMERS + 1) * 32)
-#define RD_MAX_SPLITS 16
+#define RD_MAX_SPLITS 32
 
 namespace {
 

@@ -308,7 +308,7 @@ def attention_decode_gqa(qkv, k_cache, v_cache, block_table, token_pos, token_se
     return out
 
 
-RING_DECODE_MAX_SPLITS = 16
+RING_DECODE_MAX_SPLITS = 32
 
 
 def attention_decode_ring_supported(dtype, n_heads, n_kv_heads, head_dim, page_size) -> bool:
@@ -316,11 +316,32 @@ def attention_decode_ring_supported(dtype, n_heads, n_kv_heads, head_dim, page_s
             and n_heads // n_kv_heads <= 16 and page_size % 64 == 0)
 
 
-def attention_decode_ring_splits(T, n_kv_heads, max_len) -> int:
-    """Blocks per (token, kv head): as many as fill the GPU once (two blocks per SM), at most
-    one per 64-key tile of the longest sequence and at most 16."""
+def attention_decode_ring_splits(T, n_kv_heads, max_len, head_dim=128) -> int:
+    """Blocks per (token, kv head), by a small model of the kernel's time fitted to measurements
+    (13B size, batch 8, context 4096, 320 pairs: 1 split 129 us, 6 splits 106 us; 160 pairs: 1 split
+    56 us, 2 splits 69 us).  Two blocks fit an SM, so 296 run at once.  Up to that number the kernel
+    streams at the memory rate once about 160 blocks are at work.  Beyond it the blocks run in
+    waves, and a last wave of few blocks still takes 0.43 of a full one (a block alone is bound by
+    what one SM can take in), so a grid a little larger than 296 is the worst and one of many waves
+    is fine again.  Splits cost their partial results and the merge (2.5 us and 0.7 us per split),
+    every wave about 1 us of start-up.  At most one split per 64-key tile and at most 32."""
+    pairs = max(1, T * n_kv_heads)
     tiles = max(1, -(-int(max_len) // 64))
-    return max(1, min(2 * N_SMS // max(1, T * n_kv_heads), tiles, RING_DECODE_MAX_SPLITS))
+    slots = 2 * N_SMS
+    stream_us = pairs * float(max_len) * head_dim * 4 / 6.6e6
+    best, best_us = 1, float("inf")
+    for n in range(1, min(tiles, RING_DECODE_MAX_SPLITS) + 1):
+        blocks = pairs * n
+        waves = blocks / slots
+        if blocks <= slots:
+            stretch = 1.0 / min(1.0, blocks / 160.0)
+        else:
+            full, rest = divmod(blocks, slots)
+            stretch = (full + (max(rest / slots, 0.43) if rest else 0.0)) / waves
+        us = stream_us * stretch + (2.5 + 0.7 * n if n > 1 else 0.0) + 1.0 * -(-blocks // slots)
+        if us < best_us - 1e-9:
+            best, best_us = n, us
+    return best
 
 
 def attention_decode_ring(qkv, k_cache, v_cache, block_table, token_pos, token_seq, n_heads, n_kv_heads,
@@ -350,7 +371,7 @@ def attention_decode_ring(qkv, k_cache, v_cache, block_table, token_pos, token_s
     out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=k_cache.device)
     for t0 in range(0, T, 65535):
         t1 = min(T, t0 + 65535)
-        n = attention_decode_ring_splits(t1 - t0, n_kv_heads, max_len) if splits is None else int(splits)
+        n = attention_decode_ring_splits(t1 - t0, n_kv_heads, max_len, head_dim) if splits is None else int(splits)
         part_acc = part_ml = None
         if n > 1:
             part_acc = torch.empty((t1 - t0, n_heads, n, head_dim), dtype=torch.float32, device=out.device)
