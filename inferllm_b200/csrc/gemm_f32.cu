@@ -22,7 +22,8 @@ gemm_f32_nt_kernel(const float* __restrict__ A, const float* __restrict__ W, flo
     const int m0 = blockIdx.y * GF_BM, n0 = blockIdx.x * GF_BN;
     const int lr = tid >> 2, lk = (tid & 3) * 4;  // loader: row within the tile, k offset
     const int ty = tid >> 4, tx = tid & 15;
-    const bool vec = ((K & 3) == 0) && ((lda & 3) == 0) && ((ldw & 3) == 0);
+    const bool vec = ((K & 3) == 0) && ((lda & 3) == 0) && ((ldw & 3) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) == 0;
     float acc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; i++)

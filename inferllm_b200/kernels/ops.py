@@ -61,6 +61,9 @@ def _need(t, name, dtype=None, dim=None):
         raise KernelError(f"{name} must be {dtype}, found {t.dtype}")
     if dim is not None and t.dim() != dim:
         raise KernelError(f"{name} must have {dim} dimensions, found shape {tuple(t.shape)}")
+    # rows of a multiple of 16 bytes are read 16 bytes at a time
+    if t.dtype.is_floating_point and t.numel() and (t.shape[-1] * t.element_size()) % 16 == 0 and t.data_ptr() % 16:
+        raise KernelError(f"{name} must start on a 16-byte boundary")
 
 
 def act_code(dtype):

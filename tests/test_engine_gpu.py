@@ -236,6 +236,58 @@ def test_all_products_on_the_package_kernels(name, model_folders, plain_logits):
         ops.set_gemm_backend("auto")
 
 
+def _drawn_configurations():
+    """Seeded configurations off the beaten sizes: head sizes in steps of 16 up to 256 (those of the
+    tensor-core kernels and others), 1..5 KV heads with 1..7 query heads each, widths that are no
+    multiple of 8, odd intermediate sizes and vocabularies."""
+    rng = np.random.default_rng(20240229)
+    out = []
+    for d in (16, 32, 48, 64, 80, 96, 128, 160, 256):
+        nkv = int(rng.integers(1, 6))
+        group = int(rng.choice([1, 2, 3, 4, 7]))
+        out.append(dict(
+            architectures=["LlamaForCausalLM"], hidden_size=int(rng.choice([36, 72, 100, 136, 200, 264, 90, 54])),
+            num_hidden_layers=int(rng.integers(1, 4)), num_attention_heads=nkv * group, num_key_value_heads=nkv,
+            head_dim=d, intermediate_size=int(rng.integers(40, 400)), vocab_size=int(rng.integers(50, 1500)),
+            rope_theta=float(rng.choice([1e4, 5e5, 1e6, 777.0])), rms_norm_eps=float(rng.choice([1e-5, 1e-6, 2e-4])),
+            max_position_embeddings=int(rng.choice([160, 192, 333])), tie_word_embeddings=bool(rng.integers(0, 2)),
+            eos_token_id=2))
+    return out
+
+
+@pytest.mark.parametrize("index", range(9))
+def test_drawn_configurations(index, tmp_path):
+    """The engine takes every size a configuration may have: whole, with its last tokens one by one
+    and in a batch of two, in both precisions against the plain implementation."""
+    import plain_llama
+
+    from inferllm_b200 import config_from_dict, write_random_model
+    cfg = _drawn_configurations()[index]
+    folder = str(tmp_path)
+    write_random_model(config_from_dict(cfg), folder, 900 + index, torch.bfloat16)
+    pcfg, pw = plain_llama.load_weights(folder)
+    rng = np.random.default_rng(index)
+    maxpos = cfg["max_position_embeddings"]
+    reqs = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (maxpos, 67, 5)]
+    refs = [plain_llama.forward(pcfg, pw, ids) for ids in reqs]
+    what = f"configuration {index}: " + ", ".join(f"{k}={cfg[k]}" for k in (
+        "hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim", "intermediate_size", "vocab_size"))
+    for dtype in DTYPES:
+        eng = make_engine(folder, dtype, max_tokens=64 * 12, max_batch=3)
+        w = whole(eng, reqs[0])
+        assert_close(w, refs[0], dtype, what + " whole")
+        t = tail_one_by_one(eng, reqs[0], tail=9)
+        assert_close(t, refs[0], dtype, what + " last 9 one by one")
+        got = in_batches(eng, reqs, [maxpos - 30, 60, 5], [[0, 1, 2]])
+        for r in range(3):
+            assert_close(got[r], refs[r], dtype, what + f" request {r} of a batch")
+        if dtype == "float32":
+            assert np.array_equal(w, t) and np.array_equal(w, got[0]), what + ": float32 logits differ between cuttings"
+        eng.check_device_errors()
+        eng.cache.check()
+        del eng
+
+
 def test_layers_of_real_width_bfloat16_against_float32():
     """Two layers with the widths of an 8B model (4096 wide, 32 heads over 8 KV heads of 128, a
     14336-wide feed-forward, 128256 words): the bfloat16 engine with its tensor-core kernels at the

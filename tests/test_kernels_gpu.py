@@ -87,6 +87,29 @@ def test_rmsnorm_refuses_rows_wider_than_a_block_can_hold():
                         1e-5, torch.float32)
 
 
+def test_operands_off_a_16_byte_boundary_are_refused():
+    """Rows of a multiple of 16 bytes are read 16 bytes at a time: a view that starts elsewhere is
+    refused before any kernel runs; rows of another width are read element by element and taken."""
+    H = 64
+    resid = torch.zeros(4 * H + 1, dtype=torch.float32, device="cuda")[1:].view(4, H)
+    w = torch.ones(H, dtype=torch.float32, device="cuda")
+    with pytest.raises(ops.KernelError, match="16-byte boundary"):
+        ops.add_rmsnorm(resid, None, w, 1e-5, torch.float32)
+    x = torch.randn(3 * 40 + 3, device="cuda")[3:].view(3, 40)
+    with pytest.raises(ops.KernelError, match="16-byte boundary"):
+        ops.gemm_f32(x, torch.randn(5, 40, device="cuda"))
+    H = 50                                            # 200-byte rows: no 16-byte accesses, any start will do
+    base = torch.randn(4 * H + 1, device="cuda")
+    resid = base[1:].view(4, H)
+    w = torch.randn(H, device="cuda")
+    ref = plain.rms_norm(f64(resid), f64(w), 1e-5)
+    got = ops.add_rmsnorm(resid, None, w, 1e-5, torch.float32)
+    assert maxrel(f64(got), ref) < 1e-5
+    x = torch.randn(3 * 37 + 1, device="cuda")[1:].view(3, 37)
+    wt = torch.randn(6 * 37 + 1, device="cuda")[1:].view(6, 37)
+    assert maxrel(f64(ops.gemm_f32(x, wt)), f64(x) @ f64(wt).T) < 1e-5
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T,I", [(1, 176), (9, 11008), (300, 100), (70000, 8)])
 def test_swiglu(dtype, T, I):
