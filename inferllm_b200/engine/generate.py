@@ -90,7 +90,7 @@ def generate(backend, prompts: Sequence[Sequence[int]], choose: Callable, max_ne
     for batch in res.batches:
         slots = {r: backend.new_sequence() for r in batch}
         hist = {r: list(prompts[r]) for r in batch}
-        live = list(batch)
+        live = _longest_first(batch, prompts)
         try:
             t0 = clock()
             logits = backend.step([StepItem(slots[r], list(prompts[r]), [len(prompts[r]) - 1])
@@ -161,11 +161,12 @@ def generate_pipelined(backend, prompts: Sequence[Sequence[int]], choose: Callab
         n_fed = {r: len(prompts[r]) for r in batch}          # tokens of r that the cache holds
         try:
             t0 = clock()
-            logits = backend.step([StepItem(slots[r], list(prompts[r]), [len(prompts[r]) - 1]) for r in batch])
+            order = _longest_first(batch, prompts)
+            logits = backend.step([StepItem(slots[r], list(prompts[r]), [len(prompts[r]) - 1]) for r in order])
             # (the prompts go with the first call: a sampler that penalises repetitions starts its
             # windows of last tokens from them and keeps them on the device from then on)
-            pending, pending_toks = list(batch), choose(logits, batch, [0] * len(batch),
-                                                        [list(prompts[r]) for r in batch])
+            pending, pending_toks = order, choose(logits, order, [0] * len(order),
+                                                  [list(prompts[r]) for r in order])
             # the copy of the tokens to the host starts behind the sampling and is waited for by
             # itself, not by the stream (which by then holds the next step); `pending_sel` picks the
             # sequences that are still pending out of what was copied
@@ -226,6 +227,14 @@ def generate_pipelined(backend, prompts: Sequence[Sequence[int]], choose: Callab
             for s in slots.values():
                 backend.end_sequence(s)
     return res
+
+
+def _longest_first(batch, prompts):
+    """The requests of a batch in the order in which they are stepped: the longest prompt first
+    (all grow by one token per step, so the order holds).  The attention kernels hand out their
+    blocks in the order of the step's sequences, and the blocks with the most keys should start
+    first; results are kept by request, so nothing else depends on the order."""
+    return sorted(batch, key=lambda r: -len(prompts[r]))
 
 
 def _start_read(backend, toks):
