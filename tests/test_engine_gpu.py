@@ -320,6 +320,37 @@ def test_layers_of_real_width_bfloat16_against_float32():
         assert_close(b16[r], b32[r], "bfloat16", f"request {r} in a batch, real widths")
 
 
+def test_long_context(tmp_path):
+    """A prompt of 4,200 tokens in one step (33 tiles of the prompt attention kernel per head), then
+    40 tokens one by one over 66 and 67 key tiles per head, which a single sequence reads in as many
+    splits as the decode attention kernel has, against the plain implementation (the kernels' own
+    tests make single far keys stand out; here the whole path runs at that length)."""
+    import plain_llama
+
+    from inferllm_b200 import config_from_dict, write_random_model
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=128, num_hidden_layers=1, num_attention_heads=2,
+               num_key_value_heads=1, head_dim=64, intermediate_size=256, vocab_size=300, rope_theta=10000.0,
+               rms_norm_eps=1e-5, max_position_embeddings=4352, tie_word_embeddings=False, eos_token_id=2)
+    folder = str(tmp_path)
+    write_random_model(config_from_dict(cfg), folder, 77, torch.bfloat16)
+    pcfg, pw = plain_llama.load_weights(folder)
+    rng = np.random.default_rng(5)
+    ids = rng.integers(3, 300, 4240).tolist()
+    ref = plain_llama.forward(pcfg, pw, ids)[4199:]
+    for dtype in DTYPES:
+        eng = make_engine(folder, dtype, max_tokens=4352, max_batch=1)
+        s = eng.new_sequence()
+        out = [eng.step([StepItem(s, ids[:4200], [4199])])]
+        for t in ids[4200:]:
+            out.append(eng.step([StepItem(s, [t], [0])]))
+        eng.end_sequence(s)
+        got = torch.cat(out).cpu().numpy()
+        assert_close(got[:1], ref[:1], dtype, "end of a 4,200-token prompt")
+        assert_close(got[1:], ref[1:], dtype, "40 tokens one by one behind it")
+        eng.check_device_errors()
+        del eng
+
+
 def test_random_batches_against_float32():
     """Forty batches of random size (1..12), random prompt lengths (2..3000), random numbers of
     single-token steps and sequences that end at different times, on a mid-sized model with grouped
