@@ -38,7 +38,7 @@
 #define FT_KSTAGES 3
 #define FT_VSTAGES 2
 #define FT_THREADS 192       // 4 softmax warps, the MMA warp, the TMA warp
-#define FT_WAIT_LIMIT (1 << 22)
+#define FT_WAIT_CLOCKS (1LL << 31)
 #define FT_ERR_TIMEOUT 5
 #define FT_RESCALE_STEP 8.0f // how far (in powers of two) the maximum may run ahead of the reference
 
@@ -54,17 +54,25 @@ __device__ __forceinline__ void bar_expect_tx(unsigned bar, unsigned bytes) {
 __device__ __forceinline__ void bar_arrive(unsigned bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Waits for the phase with the given parity: mbarrier.try_wait suspends the thread until the phase
+// completes or a hardware time limit passes, so a waiting warp issues next to nothing (a test_wait
+// spin took issue slots from the softmax warps of its SM sub-partition, which are bound by them).
+// Bounded by about a second of clocks; false (and the error word set) when that runs out.
+__device__ __forceinline__ bool bar_try(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool bar_wait(unsigned bar, unsigned parity, int* err) {
-    for (int i = 0; i < FT_WAIT_LIMIT; i++) {
-        unsigned ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if (i > 256) __nanosleep(20);
-    }
+    if (bar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    do {
+        if (bar_try(bar, parity)) return true;
+    } while (clock64() - t0 < FT_WAIT_CLOCKS);
     atomicExch(err, FT_ERR_TIMEOUT);
     return false;
 }
@@ -145,6 +153,32 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 
 }  // namespace
+
+// Two float32 operations in one instruction (pairs in 64-bit registers) and the maximum of three:
+// the softmax warps are bound by how many instructions they issue per score, not by a pipe.
+__device__ __forceinline__ unsigned long long f2_pack(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long f2_fma(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ unsigned long long f2_add(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
 
 template <int D>
 __global__ void __launch_bounds__(FT_THREADS, 2)
@@ -333,11 +367,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // the row's maximum over this block (the scale is positive: it is applied to the maximum)
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < FT_BN; c += 4) {
-                mx0 = fmaxf(mx0, __uint_as_float(sr[c]));
-                mx1 = fmaxf(mx1, __uint_as_float(sr[c + 1]));
-                mx2 = fmaxf(mx2, __uint_as_float(sr[c + 2]));
-                mx3 = fmaxf(mx3, __uint_as_float(sr[c + 3]));
+            for (int c = 0; c < FT_BN; c += 8) {
+                mx0 = max3(mx0, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+                mx1 = max3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
+                mx2 = max3(mx2, __uint_as_float(sr[c + 4]), __uint_as_float(sr[c + 5]));
+                mx3 = max3(mx3, __uint_as_float(sr[c + 6]), __uint_as_float(sr[c + 7]));
             }
             const float m_new = fmaxf(m_ref, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2e);
             // move the reference only when the maximum has run away from it (always at the first
@@ -369,16 +403,25 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
             // P = exp2(S * scale - reference) as bfloat16 pairs over the first 32 columns of S(i)
             unsigned pr[FT_BN / 2];
-            float ps0 = 0.f, ps1 = 0.f;
+            const unsigned long long scale2 = f2_pack(scale_log2e, scale_log2e), neg_m2 = f2_pack(-m_use, -m_use);
+            unsigned long long psa = f2_pack(0.f, 0.f), psb = psa;
 #pragma unroll
-            for (int c = 0; c < FT_BN; c += 2) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c]), scale_log2e, -m_use));       // exp2(-inf) = 0
-                const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c + 1]), scale_log2e, -m_use));
-                ps0 += p0;
-                ps1 += p1;
+            for (int c = 0; c < FT_BN; c += 4) {
+                float x0, x1, x2, x3;
+                f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), scale2, neg_m2), x0, x1);
+                f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3])), scale2, neg_m2), x2, x3);
+                const float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);   // exp2(-inf) = 0
+                psa = f2_add(psa, f2_pack(p0, p1));
+                psb = f2_add(psb, f2_pack(p2, p3));
                 pr[c >> 1] = pack_bf16(p0, p1);
+                pr[(c >> 1) + 1] = pack_bf16(p2, p3);
             }
-            l_run += ps0 + ps1;
+            {
+                float a0, a1, b0, b1;
+                f2_unpack(psa, a0, a1);
+                f2_unpack(psb, b0, b1);
+                l_run += (a0 + a1) + (b0 + b1);
+            }
             tmem_st32(s_addr, pr);
             tmem_wait_st();
             // the prompt's last block may hold positions beyond the sequence: whatever the cache

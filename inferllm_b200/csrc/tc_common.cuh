@@ -8,7 +8,7 @@
 #define TC_BM 128
 #define TC_BK 64
 #define TC_THREADS 192
-#define TC_WAIT_LIMIT (1 << 22)
+#define TC_WAIT_CLOCKS (1LL << 31)
 #define TC_ERR_TIMEOUT 4
 
 __device__ __forceinline__ unsigned tc_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -20,17 +20,24 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 // Bounded wait for the phase with the given parity; false (and the error word set) on time-out.
+// mbarrier.try_wait suspends the thread until the phase completes or a hardware time limit passes,
+// so a waiting warp issues next to nothing and leaves the issue slots of its SM sub-partition to the
+// warps that have work; the bound is about a second of clocks.
+__device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* err) {
-    for (int i = 0; i < TC_WAIT_LIMIT; i++) {
-        unsigned ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if (i > 64) __nanosleep(32);
-    }
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    do {
+        if (mbar_try(bar, parity)) return true;
+    } while (clock64() - t0 < TC_WAIT_CLOCKS);
     atomicExch(err, TC_ERR_TIMEOUT);
     return false;
 }
