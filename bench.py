@@ -208,7 +208,7 @@ def run_kernels(pk, pk_src):
             emit("gemm_tc (decode)", f"{name}, {M} tokens", us, nbytes=N * K * 2)
         del ws
     # ---- prompt attention
-    for T, nh, nkv in ((512, 32, 32), (2048, 32, 32), (8192, 32, 32), (16384, 32, 32), (2048, 32, 8), (16384, 32, 8)):
+    for T, nh, nkv in ((512, 32, 32), (2048, 32, 32), (2048, 32, 8), (8192, 32, 32), (16384, 32, 32), (16384, 32, 8)):
         n_pages = T // page
         kc = torch.randn(n_pages, nkv, page, d, device=dev).bfloat16()
         vc = torch.randn_like(kc)
