@@ -21,7 +21,14 @@ class KernelError(RuntimeError):
     pass
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The current CUDA stream's handle (asked for at every launch: the short way, since a prompt
+    step of a few hundred tokens is bound by what the host spends per launch)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -61,8 +68,9 @@ def _need(t, name, dtype=None, dim=None):
         raise KernelError(f"{name} must be {dtype}, found {t.dtype}")
     if dim is not None and t.dim() != dim:
         raise KernelError(f"{name} must have {dim} dimensions, found shape {tuple(t.shape)}")
-    # rows of a multiple of 16 bytes are read 16 bytes at a time
-    if t.dtype.is_floating_point and t.numel() and (t.shape[-1] * t.element_size()) % 16 == 0 and t.data_ptr() % 16:
+    # rows of a multiple of 16 bytes are read 16 bytes at a time (the address is looked at first: it
+    # is almost always aligned, and these checks run a few hundred times per step)
+    if t.data_ptr() & 15 and t.dtype.is_floating_point and t.numel() and (t.shape[-1] * t.element_size()) % 16 == 0:
         raise KernelError(f"{name} must start on a 16-byte boundary")
 
 
@@ -151,11 +159,15 @@ def swiglu(gu):
     return out
 
 
-# Under "auto" the gate/up product of prompts (more than 128 tokens) runs on the package's SM-pair
-# kernel with the activation as its epilogue: as fast as the library's product followed by the
-# activation kernel (24.1 ms either way for a 2,048-token prompt at 7B size), and the packed
-# projection (90 MB per layer there) never goes to memory.
+# Under "auto" the gate/up product of prompts of 512 tokens and more runs on the package's SM-pair
+# kernel with the activation as its epilogue, so that the packed projection (90 MB per layer at
+# 2,048 tokens of 7B size) never goes to memory: measured on whole prompt steps of a 7B model against
+# the library's product followed by the activation kernel, 6.70 against 7.02 ms at 512 tokens, 12.2
+# against 12.8 at 1,024, 24.1 against 24.5 at 2,048.  Shorter prompts have too few tiles of 256 x 256
+# for the 74 pairs of SMs (86 at 7B size: two rounds for little more than one round's work) and take
+# the library (5.4 against 6.6 ms at 384 tokens, 4.0 against 5.1 at 130).
 GATED_PROMPTS_ON_TC = True
+GATED_PROMPTS_ON_TC_MIN_TOKENS = 512
 
 
 def linear_gated(x, w):
@@ -173,7 +185,8 @@ def linear_gated(x, w):
             _check(load().illm_gemm_bf16_tc_gated(_ptr(x), _ptr(w), _ptr(out), M, N, K,
                                                   _ptr(tc_error_word(x.device)), _stream()), "gemm_bf16_tc_gated")
             return out
-        if (_GEMM_BACKEND == "tc" or (_GEMM_BACKEND == "auto" and GATED_PROMPTS_ON_TC)) and M > 128 and N >= 256:
+        if N >= 256 and ((_GEMM_BACKEND == "tc" and M > 128) or (
+                _GEMM_BACKEND == "auto" and GATED_PROMPTS_ON_TC and M >= GATED_PROMPTS_ON_TC_MIN_TOKENS)):
             return gemm_bf16_tc2(x, w, torch.bfloat16, gated=True)
     return swiglu(linear(x, w, defer_reduce=True))
 
