@@ -80,6 +80,35 @@ def act_code(dtype):
     return _DT[dtype]
 
 
+# The library chooses a kernel for every new shape of a product, which costs a prompt step whose
+# token count it has not seen before about 4.5 ms (7B size: 9.5 to 10 ms for a prompt of a never
+# seen length of 200 to 300 tokens, 5.2 ms for one seen before), and prompts come in every length.
+# Activations of prompt steps are therefore allocated with their rows rounded up to a multiple of
+# 64, of which the caller sees the first M; `linear` hands the library the whole buffer and gives
+# back the first M rows of the result, so the library only ever sees multiples of 64.  The rows
+# beyond M are never initialised and never read back: a row of a product depends on its own row
+# of the input only.
+LIBRARY_ROW_BUCKET = 64
+
+
+def _rows(M, cols, dtype, device):
+    """An uninitialised [M, cols] activation; for prompt-sized M the head of a buffer of whole buckets."""
+    if dtype == torch.bfloat16 and M > LIBRARY_ROW_BUCKET and M % LIBRARY_ROW_BUCKET:
+        padded = -(-M // LIBRARY_ROW_BUCKET) * LIBRARY_ROW_BUCKET
+        return torch.empty((padded, cols), dtype=dtype, device=device)[:M]
+    return torch.empty((M, cols), dtype=dtype, device=device)
+
+
+def _whole_buckets(x):
+    """The buffer of whole buckets behind an activation made by `_rows`, or None."""
+    M, K = x.shape
+    if M > LIBRARY_ROW_BUCKET and M % LIBRARY_ROW_BUCKET and x.storage_offset() == 0:
+        padded = -(-M // LIBRARY_ROW_BUCKET) * LIBRARY_ROW_BUCKET
+        if x.untyped_storage().nbytes() >= padded * K * x.element_size():
+            return x.as_strided((padded, K), (K, 1))
+    return None
+
+
 def embedding(ids, table, err):
     """ids int32 [T], table [V, H] (float32 or bfloat16) -> float32 [T, H]."""
     _need(ids, "ids", torch.int32, 1)
@@ -115,7 +144,7 @@ def add_rmsnorm(resid, delta, weight, eps, out_dtype, rows=None, write_resid=Tru
     n = resid.shape[0] if rows is None else rows.numel()
     if rows is not None:
         _need(rows, "rows", torch.int32, 1)
-    y = torch.empty((n, H), dtype=out_dtype, device=resid.device)
+    y = _rows(n, H, out_dtype, resid.device)
     if partials is not None:
         _check(load().illm_add_rmsnorm_partials(
             _ptr(resid), _ptr(partials.ws), partials.splits, partials.rows * partials.cols, _ptr(weight),
@@ -145,7 +174,7 @@ def swiglu(gu):
     if isinstance(gu, SplitKPartials):
         T, I2 = gu.shape
         if I2 % 16 == 0:
-            out = torch.empty((T, I2 // 2), dtype=torch.bfloat16, device=gu.device)
+            out = _rows(T, I2 // 2, torch.bfloat16, gu.device)
             _check(load().illm_swiglu_partials(_ptr(gu.ws), gu.splits, gu.rows * gu.cols, _ptr(out), T, I2 // 2,
                                                _stream()), "swiglu_partials")
             return out
@@ -154,7 +183,7 @@ def swiglu(gu):
     T, I2 = gu.shape
     if I2 % 2:
         raise KernelError("swiglu: the packed projection must have an even number of columns")
-    out = torch.empty((T, I2 // 2), dtype=gu.dtype, device=gu.device)
+    out = _rows(T, I2 // 2, gu.dtype, gu.device)
     _check(load().illm_swiglu(_ptr(gu), _ptr(out), act_code(gu.dtype), T, I2 // 2, _stream()), "swiglu")
     return out
 
@@ -252,7 +281,7 @@ def attention_generic(qkv, k_cache, v_cache, block_table, token_pos, token_seq, 
     _need(k_cache, "k_cache", qkv.dtype, 4)
     _need(v_cache, "v_cache", qkv.dtype, 4)
     T = qkv.shape[0]
-    out = torch.empty((T, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    out = _rows(T, n_heads * head_dim, qkv.dtype, qkv.device)
     _check(load().illm_attention_generic(
         _ptr(qkv), qkv.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
         block_table.shape[1], _ptr(token_pos), _ptr(token_seq), _ptr(out), act_code(qkv.dtype), T,
@@ -281,7 +310,7 @@ def attention_decode(qkv, k_cache, v_cache, block_table, token_pos, token_seq, n
     n_chunks = max(1, -(-int(max_len) // DECODE_CHUNK))
     part_acc = torch.empty((T, n_heads, n_chunks, head_dim), dtype=torch.float32, device=qkv.device)
     part_ml = torch.empty((T, n_heads, n_chunks, 2), dtype=torch.float32, device=qkv.device)
-    out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    out = _rows(T, n_heads * head_dim, torch.bfloat16, qkv.device)
     for t0 in range(0, T, 65535):
         t1 = min(T, t0 + 65535)
         _check(load().illm_attention_decode(
@@ -313,7 +342,7 @@ def attention_decode_gqa(qkv, k_cache, v_cache, block_table, token_pos, token_se
     n_chunks = max(1, -(-int(max_len) // GQA_DECODE_CHUNK))
     part_acc = torch.empty((T, n_heads, n_chunks, head_dim), dtype=torch.float32, device=qkv.device)
     part_ml = torch.empty((T, n_heads, n_chunks, 2), dtype=torch.float32, device=qkv.device)
-    out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    out = _rows(T, n_heads * head_dim, torch.bfloat16, qkv.device)
     for t0 in range(0, T, 65535):
         t1 = min(T, t0 + 65535)
         _check(load().illm_attention_decode_gqa(
@@ -434,7 +463,7 @@ def attention_prefill(qkv, k_cache, v_cache, block_table, cu_q, seq_lens, max_q,
     _need(k_cache, "k_cache", torch.bfloat16, 4)
     _need(v_cache, "v_cache", torch.bfloat16, 4)
     T, B = qkv.shape[0], seq_lens.numel()
-    out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    out = _rows(T, n_heads * head_dim, torch.bfloat16, qkv.device)
     _check(load().illm_attention_prefill(
         _ptr(qkv), qkv.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(cu_q), _ptr(seq_lens), _ptr(out), B, int(max_q), n_heads, n_kv_heads, head_dim, page_size,
@@ -455,7 +484,7 @@ def attention_prefill_tc(qkv, k_cache, v_cache, block_table, cu_q, seq_lens, max
     _need(k_cache, "k_cache", torch.bfloat16, 4)
     _need(v_cache, "v_cache", torch.bfloat16, 4)
     T, B = qkv.shape[0], seq_lens.numel()
-    out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    out = _rows(T, n_heads * head_dim, torch.bfloat16, qkv.device)
     _check(load().illm_attention_prefill_tc(
         _ptr(qkv), qkv.shape[1], T, _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table),
         block_table.shape[1], _ptr(cu_q), _ptr(seq_lens), _ptr(out), B, int(max_q), n_heads, n_kv_heads,
@@ -601,7 +630,7 @@ def gemm_bf16_tc2(x, w, out_dtype=torch.bfloat16, gated=False):
     if K % 8 or x.data_ptr() % 16 or w.data_ptr() % 16 or (gated and N % 2):
         raise KernelError(f"gemm_bf16_tc2: K = {K} must be a multiple of 8, the operands 16-byte aligned"
                           " and a gated weight an even number of rows")
-    out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
+    out = _rows(M, N // 2 if gated else N, out_dtype, x.device)
     _check(load().illm_gemm_bf16_tc2(_ptr(x), _ptr(w), _ptr(out), act_code(out_dtype), 1 if gated else 0, M, N, K,
                                      _ptr(tc_error_word(x.device)), _stream()), "gemm_bf16_tc2")
     return out
@@ -639,9 +668,11 @@ def linear(x, w, out_dtype=None, defer_reduce=False):
         if M > 128 and w.shape[0] >= 256:
             return gemm_bf16_tc2(x, w, out_dtype or torch.bfloat16)      # prompts: pairs of SMs
         return gemm_bf16_tc(x, w, out_dtype or torch.bfloat16, defer_reduce=defer_reduce)
-    if out_dtype == torch.float32:
-        return torch.mm(x, w.t(), out_dtype=torch.float32)
-    return torch.mm(x, w.t())
+    whole = _whole_buckets(x)
+    if whole is not None:
+        x = whole
+    out = torch.mm(x, w.t(), out_dtype=torch.float32) if out_dtype == torch.float32 else torch.mm(x, w.t())
+    return out[:M] if whole is not None else out
 
 
 def argmax(logits):
