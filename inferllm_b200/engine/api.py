@@ -139,6 +139,10 @@ class Model:
                 f"Average Token Compute Time: {per:.3f}ms\n"
                 f"Average Token Generation Speed: {rate:.3f}token/s\n")
 
+    def warm_up(self, prompt_tokens: int = 0, batch_sizes: Sequence[int] = ()) -> None:
+        """Before the first request: run what costs extra the first time (see `Engine.warm_up`)."""
+        self.engine.warm_up(prompt_tokens, batch_sizes)
+
     # ---- batches of requests
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 128,

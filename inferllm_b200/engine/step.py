@@ -335,6 +335,35 @@ class Engine:
             return buf[:n].tolist()
         return result
 
+    def warm_up(self, prompt_tokens: int = 0, batch_sizes: Sequence[int] = ()) -> None:
+        """Pay what is paid once, before the first request: a prompt step for every bucket of 64
+        tokens up to `prompt_tokens` (the library chooses its kernels per shape of a product, about
+        10 ms each at 7B size), and for every batch size three one-token steps, of which the second
+        captures the CUDA graph that later steps of that size replay.  Uses free slots and pages
+        only and gives them back; sizes that do not fit the cache are left out."""
+        lim = self.limits()
+        longest = min(int(prompt_tokens), lim.max_seq_len, lim.num_pages * lim.page_size)
+        for n in range(ops.LIBRARY_ROW_BUCKET, longest + 1, ops.LIBRARY_ROW_BUCKET):
+            slot = self.new_sequence()
+            try:
+                self.step([StepItem(slot, [0] * n, [n - 1])])
+            except CacheError:              # live sequences hold the pages: no larger size fits either
+                break
+            finally:
+                self.end_sequence(slot)
+        for b in batch_sizes:
+            if b < 1 or b > lim.max_batch or b > lim.num_pages or self.cache.slots.n_free < b:
+                continue
+            slots = [self.new_sequence() for _ in range(b)]
+            try:
+                self.step([StepItem(s, [0], [0]) for s in slots])
+                for _ in range(3):
+                    self.step([StepItem(s, [0], [0]) for s in slots])
+            finally:
+                for s in slots:
+                    self.end_sequence(s)
+        torch.cuda.current_stream().synchronize()
+
     def check_device_errors(self) -> None:
         """Read the kernels' error word (synchronises)."""
         code = int(self.err.item())

@@ -39,6 +39,23 @@ def test_greedy_generation_matches_plain(name, lens, n_new, model_folders, plain
     assert all(g[0] == w_[0] for g, w_ in zip(got, want))
 
 
+def test_warm_up_changes_nothing_and_gives_everything_back(model_folders, plain_models):
+    """`Model.warm_up` runs prompt steps of every bucket and captures the graphs of the batch sizes
+    asked for; afterwards all slots and pages are free and generation gives the same tokens."""
+    name = "C"
+    cfg, w = plain_models[name]
+    prompts = [random_prompt(name, n, 70 + n) for n in (130, 9)]
+    want = [plain.greedy_generate(cfg, w, p, 6) for p in prompts]
+    m = load(model_folders[name], "float32", nr_ctx=TINY[name]["max_position_embeddings"], max_tokens=1024)
+    m.init(0, 1.0, 0.0, 1.0, 0, 0, -1)
+    m.warm_up(prompt_tokens=300, batch_sizes=(1, 2, 5000))
+    cache = m.engine.cache
+    cache.check()
+    assert cache.slots.n_free == cache.num_slots and cache.pages_free() == [cache.num_pages]
+    assert any(isinstance(v, tuple) for v in m.engine._graphs.values()), "no graph was captured"
+    assert m.generate(prompts, max_new_tokens=6, stop_ids=[]).tokens == want
+
+
 def test_stop_token_ends_early_and_batches_follow_each_other(model_folders, plain_models):
     name = "A"
     cfg, w = plain_models[name]
