@@ -24,6 +24,9 @@ from ..parts.base import Runtime
 from ..registry import config_from_folder, get_architecture
 from ..weights import init_random_weights, load_model_weights
 
+PROMPT_BUCKET = 64                # tokens; also the rows the library's products are rounded up to
+PROMPT_GRAPH_MAX_TOKENS = 1024    # longer prompts keep the GPU busy longer than the host needs to issue them
+
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "fp32": torch.float32}
 
@@ -146,6 +149,7 @@ class Engine:
         self._tok_bufs, self._tok_next = [None] * 4, 0   # pinned buffers for sampled tokens on their way to the host
         self._stage_next = 0
         self._graphs = {}
+        self._pad_safe = None          # whether single prompts may be padded and replayed (asked once)
         self._graph_pool = None
         self.loaded = False
 
@@ -266,6 +270,11 @@ class Engine:
         if device_ids is not None and (len(ids) != len(items) or device_ids.numel() != len(items)
                                        or device_ids.dtype != torch.int32):
             raise EngineError("device_ids needs one int32 id per item and items of one token each")
+        if (self.options.cuda_graphs and len(items) == 1 and 1 < len(ids) <= PROMPT_GRAPH_MAX_TOKENS
+                and self._pads_prompts()):
+            logits = self._prompt_step_graphed(items[0].slot, ids, want_rows)
+            if logits is not None:
+                return logits
         plan = self.cache.plan_step([it.slot for it in items], [len(it.tokens) for it in items])
         if self.options.cuda_graphs and len(ids) == len(items) and self.model.graph_safe():
             logits = self._decode_step_graphed(plan, ids, want_rows, device_ids)
@@ -276,6 +285,62 @@ class Engine:
             logits = self.model.forward(ctx)
         self.cache.commit_step(plan)
         return logits
+
+    def _pads_prompts(self) -> bool:
+        if self._pad_safe is None:
+            self._pad_safe = bool(self.model.pad_safe())
+        return self._pad_safe
+
+    def _prompt_step_graphed(self, slot: int, ids, want_rows) -> Optional[torch.Tensor]:
+        """A single prompt (or a further piece of one sequence) of up to 1,024 tokens: the host needs
+        longer to issue the step's launches than the GPU to run them, so the step is padded to whole
+        buckets of 64 tokens, with tokens behind the real ones that no real token sees (what they
+        leave in the sequence's pages lies behind its length and is overwritten by the tokens that
+        follow), and the launches of a bucket are captured in a CUDA graph the second time it is
+        seen.  Only where the padding needs no page that the step would not need anyway and stays
+        within the longest sequence; None otherwise (the caller then runs the step as it is).  The
+        logits of the real tokens do not depend on the padding beyond rounding, and in float32 not
+        at all."""
+        c = self.cache
+        T = len(ids)
+        padded = -(-T // PROMPT_BUCKET) * PROMPT_BUCKET
+        past = c.seq_len[slot] if c.slots.is_held(slot) else 0
+        if not c.slots.is_held(slot) or past + padded > c.max_seq_len:
+            return None
+        if any(g.ledger.pages_needed(slot, past + padded) != g.ledger.pages_needed(slot, past + T) for g in c.paged):
+            return None
+        plan = c.plan_step([slot], [padded])
+        ids = list(ids) + [0] * (padded - T)
+        key = ("prompt", padded, len(want_rows))
+        entry = self._graphs.get(key)
+        if entry is None or entry == "seen":
+            ctx = StepContext(self, plan, ids, want_rows)
+            if entry is None:
+                self._graphs[key] = "seen"
+                out = self.model.forward(ctx)
+            else:
+                if len(self._graphs) > 64:
+                    self._graphs = {k: v for k, v in self._graphs.items() if v == "seen"}
+                torch.cuda.current_stream().synchronize()
+                graph = torch.cuda.CUDAGraph()
+                before = ops.launch_count()
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    out = self.model.forward(ctx)
+                launches = ops.launch_count() - before
+                if self._graph_pool is None:
+                    self._graph_pool = graph.pool()
+                self._graphs[key] = (graph, ctx, out, launches)
+                graph.replay()
+                out = out.clone()
+        else:
+            graph, ctx, out, launches = entry
+            StepContext(self, plan, ids, want_rows, into=ctx.buffer)
+            graph.replay()
+            ops.count_launches(launches)
+            out = out.clone()
+        plan.q_lens = [T]               # the sequence grows by its real tokens only
+        c.commit_step(plan)
+        return out
 
     def _decode_step_graphed(self, plan, ids, want_rows, device_ids=None) -> torch.Tensor:
         """One token per sequence: the launches of such a step are the same every time (all that
@@ -336,21 +401,24 @@ class Engine:
         return result
 
     def warm_up(self, prompt_tokens: int = 0, batch_sizes: Sequence[int] = ()) -> None:
-        """Pay what is paid once, before the first request: a prompt step for every bucket of 64
+        """Pay what is paid once, before the first request: prompt steps for every bucket of 64
         tokens up to `prompt_tokens` (the library chooses its kernels per shape of a product, about
-        10 ms each at 7B size), and for every batch size three one-token steps, of which the second
-        captures the CUDA graph that later steps of that size replay.  Uses free slots and pages
+        10 ms each at 7B size; the second step of a bucket of up to 1,024 tokens captures its CUDA
+        graph), and for every batch size three one-token steps, of which the second captures the
+        graph that later steps of that size replay.  Uses free slots and pages
         only and gives them back; sizes that do not fit the cache are left out."""
         lim = self.limits()
         longest = min(int(prompt_tokens), lim.max_seq_len, lim.num_pages * lim.page_size)
         for n in range(ops.LIBRARY_ROW_BUCKET, longest + 1, ops.LIBRARY_ROW_BUCKET):
-            slot = self.new_sequence()
             try:
-                self.step([StepItem(slot, [0] * n, [n - 1])])
+                for _ in range(2 if n <= PROMPT_GRAPH_MAX_TOKENS else 1):     # the second sight of a bucket captures its graph
+                    slot = self.new_sequence()
+                    try:
+                        self.step([StepItem(slot, [0] * n, [n - 1])])
+                    finally:
+                        self.end_sequence(slot)
             except CacheError:              # live sequences hold the pages: no larger size fits either
                 break
-            finally:
-                self.end_sequence(slot)
         for b in batch_sizes:
             if b < 1 or b > lim.max_batch or b > lim.num_pages or self.cache.slots.n_free < b:
                 continue

@@ -89,3 +89,8 @@ class DecoderModel:
         part reads host-side fields of the step context (a mixer says so with `graph_safe`)."""
         return all(getattr(b.mixer, "graph_safe", False) and getattr(b.ffn, "graph_safe", True)
                    for b in self.blocks)
+
+    def pad_safe(self) -> bool:
+        """True if a single prompt may be run with tokens appended behind its own (see
+        `parts.Mixer.pad_safe`) and launches the same kernels for the same token count."""
+        return self.graph_safe() and all(getattr(b.mixer, "pad_safe", False) for b in self.blocks)

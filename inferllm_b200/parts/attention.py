@@ -24,6 +24,13 @@ from .base import Mixer, PagedKV, TensorDecl, build_part, register_mixer
 class Attention(Mixer):
     graph_safe = True   # a decode step's launches depend only on the batch size
 
+    @property
+    def pad_safe(self) -> bool:
+        """Causal attention: tokens behind a sequence's real ones are seen by none of them.  Said
+        only for the plain case: no window, and a position encoding that is nothing but the table
+        rotation (any other runs code of its own, which is not known to launch the same kernels)."""
+        return self.window is None and self.position.rotation_table() is not None
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.hidden = int(spec["hidden_size"])

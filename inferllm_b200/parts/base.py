@@ -121,6 +121,13 @@ class Mixer(Part):
     # fields of the step context (q_lens, past, ...) leaves it False.
     graph_safe = False
 
+    # True when tokens appended behind a sequence's real tokens in a step change nothing that is
+    # kept (they may leave keys and values behind the sequence's length in its own pages, which the
+    # next tokens overwrite) and nothing the real tokens get back, and when a step of many tokens
+    # of one sequence launches the same kernels whenever the token count is the same.  The engine
+    # then pads single prompts to whole buckets of tokens and replays them from captured graphs.
+    pad_safe = False
+
     def cache_request(self):
         """`PagedKV`, `FixedState` or None."""
         return None
