@@ -175,6 +175,39 @@ def test_wanted_places_and_padding_free_batches(dtype, model_folders, plain_logi
         eng.end_sequence(s)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_single_prompts_padded_and_replayed_from_graphs(dtype, model_folders, plain_logits):
+    """A single prompt is padded to whole buckets of 64 tokens behind its real ones and, from the
+    second time a bucket is seen, captured and replayed.  Three rounds (issued, captured, replayed)
+    of: a prompt of 100 tokens, a second piece of 100 tokens behind 128 (padded to 128: its padding
+    leaves keys behind the sequence's length, in pages the sequence holds anyway), then single
+    tokens that overwrite them.  Every logit matches the plain implementation, and in float32 the
+    three rounds agree bit for bit."""
+    name = "C"
+    ids = random_prompt(name, 300, 9)
+    ref = plain_logits(name, ids)
+    eng = make_engine(model_folders[name], dtype, max_tokens=1024, max_batch=2)
+    rounds = []
+    for _ in range(3):
+        s = eng.new_sequence()
+        out = [eng.step([StepItem(s, ids[:100], list(range(100)))]),
+               eng.step([StepItem(s, ids[100:128], list(range(28)))]),
+               eng.step([StepItem(s, ids[128:228], list(range(100)))])]
+        assert eng.sequence_length(s) == 228
+        for t in ids[228:]:
+            out.append(eng.step([StepItem(s, [t], [0])]))
+        eng.end_sequence(s)
+        rounds.append(torch.cat(out).cpu().numpy())
+        assert_close(rounds[-1], ref, dtype, f"round {len(rounds)}")
+    if dtype == "float32":
+        assert np.array_equal(rounds[0], rounds[1]) and np.array_equal(rounds[0], rounds[2])
+    captured = [k for k, v in eng._graphs.items() if isinstance(v, tuple) and k[0] == "prompt"]
+    assert ("prompt", 128, 100) in captured, captured
+    eng.check_device_errors()
+    eng.cache.check()
+    assert eng.cache.slots.n_free == eng.cache.num_slots
+
+
 def test_result_does_not_depend_on_the_slot_or_on_old_cache_contents(model_folders):
     """float32, bit for bit: a request gives the same logits in a fresh cache, in another slot,
     and in pages that other requests have filled before."""
