@@ -183,3 +183,17 @@ def test_pipelined_loop_makes_the_same_decisions(max_new, stop, max_seq):
     again = generate_pipelined(c, prompts, tensor_script(script), max_new, stop)
     assert again.tokens == want.tokens and again.finish == want.finish and c.len == {}
     assert c.reads >= 1
+
+
+@pytest.mark.parametrize("loop,script_of", [(generate, scripted), (generate_pipelined, tensor_script)])
+def test_a_batch_is_stepped_longest_prompt_first(loop, script_of):
+    """Both loops put a batch's sequences into every step longest first (the attention kernels hand
+    out their blocks in that order) and keep the results by request."""
+    prompts = [[1], [1, 2, 3, 4, 5], [1, 2], [1, 2, 3]]
+    script = {r: [10 + r] * 3 for r in range(4)}
+    be = FakeBackend(max_batch=4, num_pages=16, page_size=4, max_seq_len=16)
+    res = loop(be, prompts, script_of(script), 3, [])
+    assert res.tokens == [[10 + r] * 3 for r in range(4)]
+    assert [n for _, n in be.log[0]] == [5, 3, 2, 1]               # the prompts, longest first
+    first = [slot for slot, _ in be.log[0]]
+    assert all([slot for slot, _ in step] == first for step in be.log[1:3])   # and so in the steps after
