@@ -150,6 +150,7 @@ class Engine:
         self._stage_next = 0
         self._graphs = {}
         self._pad_safe = None          # whether single prompts may be padded and replayed (asked once)
+        self._graphs_backend = None    # `kernels.ops.gemm_backend()` when the graphs were captured
         self._graph_pool = None
         self.loaded = False
 
@@ -252,6 +253,9 @@ class Engine:
             raise EngineError("the model has no weights yet")
         if not items:
             raise EngineError("a step needs at least one sequence")
+        if ops.gemm_backend() != self._graphs_backend:
+            # the choice of product kernels is process-wide and part of what a graph captured
+            self._graphs, self._graphs_backend = {}, ops.gemm_backend()
         ids, want_rows, off = [], [], 0
         for it in items:
             n = len(it.tokens)

@@ -640,6 +640,11 @@ _GEMM_BACKEND = "auto"
 GEMM_TC_MAX_TOKENS_AUTO = 16
 
 
+def gemm_backend() -> str:
+    """Which kernels run the bfloat16 products now (`set_gemm_backend`)."""
+    return _GEMM_BACKEND
+
+
 def set_gemm_backend(name: str) -> None:
     """Which kernel runs the bfloat16 matrix products.  "tc": the package's tcgen05 kernels for
     every product they can take (K a multiple of 8): `gemm_tc.cu` up to 128 tokens, the SM-pair
