@@ -2,16 +2,18 @@
 """Benchmark of inferllm_b200 on one B200: decode tokens per second of a LLaMA-2-7B-sized
 model with random weights (the headline: batch 8 at the end of a 4096-token context), the same
 through the Python entry point with host tokens in and out, a 2,048-token prefill, and decode
-at batch 1 and 64.  Prints ONE JSON line.
+at batch 1 and 64 at the start, the middle and the end of the context.  Prints ONE JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
 A "step" is one decode step of the whole batch.  Timing is by CUDA events on the launching
 stream after the warm-up steps; every step reads all weights (13 GB, far larger than the L2),
 so nothing is served from cache between steps.  The reference (MegEngine/InferLLM) publishes
-only CPU int4 numbers for this architecture (docs/profile.md: 3.2-12.7 tok/s), has no GPU
-number, no batch above 1 and cannot be pip-installed, so `vs_baseline` is null and
-`--impl reference` reports why it is unavailable.
+only CPU int4 numbers for this architecture (docs/profile.md: 3.2-12.7 tok/s) and no GPU number,
+so `vs_baseline` is null.  `--impl reference` builds the unmodified reference with its own CMake
+files and times its public `Model` API (baseline/reference_arm.py): float32, one sequence, a
+model of the same layer sizes with 4 of the 32 layers; `points.ref_like_*` of this program's own
+line are measured at exactly that configuration.
 """
 import argparse
 import json
@@ -24,12 +26,13 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: LLaMA-2-7B size, benchmark context 4096
+# LLaMA-2-7B size (32 layers of width 4096, 32 heads of 128, feed-forward 11008, 32000 words), context 4096
 CONFIG_7B = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidden_layers=32,
                  num_attention_heads=32, num_key_value_heads=32, head_dim=128,
                  intermediate_size=11008, vocab_size=32000, rope_theta=10000.0, rms_norm_eps=1e-5,
                  max_position_embeddings=4096, tie_word_embeddings=False)
-# BASELINE.json configs[3] and configs[4], for runs beside the default one (--model 8b / 13b)
+# Llama-3-8B size (8 KV heads, feed-forward 14336, 128256 words) and LLaMA-2-13B size (40 layers of
+# width 5120), for runs beside the default one (--model 8b / 13b)
 CONFIG_8B = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidden_layers=32,
                  num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336,
                  vocab_size=128256, rope_theta=500000.0, rms_norm_eps=1e-5, max_position_embeddings=8192,
@@ -107,6 +110,11 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
+def _has(program):
+    import shutil
+    return shutil.which(program) is not None
+
+
 def model_figures(cfg, n_layers):
     """Bytes and flops of one step, from the configuration."""
     H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
@@ -127,7 +135,8 @@ def prefill_flops(cfg, n_layers, T, fig):
     return linear + attn
 
 
-SCENARIOS = {"8b": "16:64:2048:256", "13b": "32:128:1024:256", "7b": "8:512:512:256"}
+SCENARIOS = {"8b": "16:64:2048:256", "13b": "32:128:1024:to4096", "7b": "8:512:512:256"}
+REF_LIKE_LAYERS = 4            # layers of the model that the reference arm runs (baseline/reference_arm.py)
 
 
 def run_kernels(pk, pk_src):
@@ -268,9 +277,12 @@ def run_scenario(args, cfg, cfgd, model_name, L, fig, pk, pk_src):
     from inferllm_b200.kernels import ops
 
     spec = SCENARIOS[args.model] if args.scenario == "config" else args.scenario
-    B, lo, hi, new = (int(x) for x in spec.split(":"))
+    B, lo, hi = (int(x) for x in spec.split(":")[:3])
     g = torch.Generator().manual_seed(0)
     lens = torch.randint(lo, hi + 1, (B,), generator=g).tolist()
+    new = spec.split(":")[3]
+    # "toN": every sequence decodes until the longest prompt's sequence stands at position N
+    new = int(new[2:]) - max(lens) - 1 if new.startswith("to") else int(new)
     prompts = [torch.randint(0, cfgd["vocab_size"], (n,), generator=g).tolist() for n in lens]
     ctx = max(lens) + new + 1
     max_tokens = sum(-(-(n + new + 1) // 64) * 64 for n in lens) + 64
@@ -288,7 +300,7 @@ def run_scenario(args, cfg, cfgd, model_name, L, fig, pk, pk_src):
     pf_flops = sum(prefill_flops(cfgd, L, n, fig) for n in lens)
     print(json.dumps({
         "scenario": spec, "model": model_name, "layers": L, "batch": B, "prompt_lengths": [min(lens), max(lens)],
-        "prompt_tokens": sum(lens), "new_tokens_each": new,
+        "prompt_tokens": sum(lens), "new_tokens_each": new, "last_position": max(lens) + new,
         "prefill": {"tokens_per_s": round(res.prefill_tokens / res.prefill_s, 1), "ms": round(res.prefill_s * 1e3, 2),
                     "frac": round(pf_flops / res.prefill_s / (pk["bf16_tflops"] * 1e12), 4)},
         "decode": {"tokens_per_s": round(B / dec_ms * 1e3, 1), "ms_per_step": round(dec_ms, 4),
@@ -308,7 +320,7 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--only", choices=["decode", "prefill"], help="run one scenario (for profiling); "
                     "prints a short JSON line of that scenario only")
-    ap.add_argument("--model", default="7b", choices=sorted(MODELS), help="sizes of BASELINE.json configs[2..4]")
+    ap.add_argument("--model", default="7b", choices=sorted(MODELS), help="LLaMA-2-7B (default), Llama-3-8B or LLaMA-2-13B sizes")
     ap.add_argument("--gemm", default="auto", choices=["auto", "tc", "library"])
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels without programmatic dependent launch")
     ap.add_argument("--context", type=int, default=CONTEXT, help="position at which the timed decode steps end")
@@ -316,17 +328,23 @@ def main():
                     "several sizes, one JSON line each")
     ap.add_argument("--scenario", metavar="B:MIN:MAX:NEW", help="beside the contract: B prompts of random ids with "
                     "lengths uniform in [MIN, MAX] (seeded) prefilled in one step of unequal lengths, then NEW tokens "
-                    "each, through the Python entry point; 'config' = the workload BASELINE.json names for --model "
-                    "(8b: 16:64:2048:256, 13b: 32:128:1024:256 of its 3072+ steps)")
+                    "each (or 'toN': until position N), through the Python entry point; 'config' = the workload of --model "
+                    "(8b: 16:64:2048:256, 13b: 32:128:1024:to4096)")
     args = ap.parse_args()
 
     if args.gpus != 1:
         print(f"bench.py: inferllm_b200 is a single-GPU library; --gpus {args.gpus} is not supported (N=1 only)")
         return 2
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "MegEngine/InferLLM is a CMake C++ project, not a Python package: pip reports "
-                          "'neither setup.py nor pyproject.toml found'; it also has no batch > 1 and no bf16 path"}))
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import reference_arm
+        gpu = subprocess.run(["nvidia-smi", "-L"], capture_output=True).returncode == 0 if _has("nvidia-smi") else False
+        with ClockSampler() as cs:
+            line = reference_arm.run(args.steps, args.warmup, layers=REF_LIKE_LAYERS, gpu_visible=gpu)
+        if "unavailable" not in line:
+            line["clocks"] = cs.summary()
+            line["gpu_launches"] = 0        # none of this repository's kernels run in the reference arm
+        print(json.dumps(line))
         return 0
     K, W = args.steps, max(3, args.warmup)
 
@@ -351,12 +369,15 @@ def main():
     if args.scenario:
         return run_scenario(args, cfg, cfgd, model_name, L, fig, pk, pk_src)
 
-    # one engine for every scenario: cache for the batch at full context, or 64 short sequences
+    # one engine for every scenario: cache for 64 sequences at the full context (137 GB at 7B size),
+    # or for the batch alone where only that is run
     decode_room = K + W + 8
     if args.only == "decode":           # one scenario: room for the batch at the context asked for
         max_tokens = B * (-(-(args.context + 8) // 64) * 64) + 64
+    elif args.skip_points:
+        max_tokens = max(B * CONTEXT, PREFILL_TOKENS) + 64
     else:
-        max_tokens = max(B * CONTEXT, 64 * (-(-(512 + decode_room) // 64) * 64), PREFILL_TOKENS) + 64
+        max_tokens = max(B, 64) * CONTEXT + 64
     model = Model(ModelConfig(compt_type="bfloat16", nr_ctx=CONTEXT, max_tokens=max_tokens, max_batch=max(B, 64)))
     model.load_random(cfg, seed=0)
     ops.set_gemm_backend(args.gemm)
@@ -366,8 +387,8 @@ def main():
     eng = model.engine
     g = torch.Generator().manual_seed(0)
 
-    def rand_ids(n):
-        return torch.randint(0, cfgd["vocab_size"], (n,), generator=g).tolist()
+    def rand_ids(n, vocab=cfgd["vocab_size"]):
+        return torch.randint(0, vocab, (n,), generator=g).tolist()
 
     def timed(fn, n):
         torch.cuda.synchronize()
@@ -380,32 +401,39 @@ def main():
         return e0.elapsed_time(e1) / n
 
     # ---- decode: `batch` sequences, timed steps end at position `ctx_end`
-    def decode_run(batch, ctx_end, steps, warm):
+    def decode_run(engine, batch, ctx_end, steps, warm):
         start = ctx_end - steps - warm
-        slots = [eng.new_sequence() for _ in range(batch)]
+        slots = [engine.new_sequence() for _ in range(batch)]
         per_step = max(1, 8192 // start)                  # prompts go in steps of about 8k tokens
         for i in range(0, batch, per_step):
-            eng.step([StepItem(s, rand_ids(start), []) for s in slots[i:i + per_step]])
+            engine.step([StepItem(s, rand_ids(start), []) for s in slots[i:i + per_step]])
         toks = [[t] for t in rand_ids(batch)]
 
         def one():
-            eng.step([StepItem(s, t, [0]) for s, t in zip(slots, toks)])
+            engine.step([StepItem(s, t, [0]) for s, t in zip(slots, toks)])
 
         for _ in range(warm):
             one()
         before = ops.launch_count()
-        with ClockSampler() as cs:
-            ms = timed(one, steps)
+        ms = timed(one, steps)
         launches = ops.launch_count() - before
         for s in slots:
-            eng.end_sequence(s)
-        return ms, launches, cs.summary()
+            engine.end_sequence(s)
+        return ms, launches
+
+    def hbm_frac(figures, batch, ctx_end, steps, ms):
+        nbytes = figures["weight_bytes"] + batch * (ctx_end - steps // 2) * figures["kv_bytes_per_token"]
+        return nbytes, nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]
 
     if args.only == "decode":
-        ms, launches, clocks = decode_run(B, args.context, K, W)
+        ms, launches = decode_run(eng, B, args.context, K, W)
         print(json.dumps({"only": "decode", "batch": B, "layers": L, "context": args.context,
                           "ms_per_step": round(ms, 4), "gpu_launches": launches}))
         return 0
+
+    # the clocks are sampled over all timed regions together (one region alone is a tenth of a second)
+    sampler = ClockSampler()
+    sampler.__enter__()
 
     # ---- prefill of one 2,048-token prompt
     prompt = rand_ids(PREFILL_TOKENS)
@@ -419,6 +447,7 @@ def main():
         prefill_once()
     pf_ms = timed(prefill_once, 3)
     if args.only == "prefill":
+        sampler.__exit__()
         print(json.dumps({"only": "prefill", "layers": L, "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3)}))
         return 0
     pf_flops = prefill_flops(cfgd, L, PREFILL_TOKENS, fig)
@@ -427,14 +456,12 @@ def main():
                "frac_of_sustained": round(pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4),
                "tflops": round(pf_flops / (pf_ms * 1e-3) / 1e12, 1)}
 
-    ms, launches, clocks = decode_run(B, CONTEXT, K, W)
+    ms, launches = decode_run(eng, B, CONTEXT, K, W)
     value = B / ms * 1e3
-    ctx_mid = CONTEXT - K // 2
-    step_bytes = fig["weight_bytes"] + B * ctx_mid * fig["kv_bytes_per_token"]
+    step_bytes, frac = hbm_frac(fig, B, CONTEXT, K, ms)
     achieved = step_bytes / (ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk_src,
-                "bytes_per_step": step_bytes}
+                "frac": round(frac, 4), "peak_source": pk_src, "bytes_per_step": step_bytes}
 
     # ---- the same through the Python entry point: host token ids in, host token ids out, every
     # step; W warm-up steps after the prompt, then K timed steps that end at the same position
@@ -450,14 +477,36 @@ def main():
     e2e = {"value": round(e2e_val, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B,
            "steps": len(timed_steps), "warmup": res.decode_steps - len(timed_steps)}
 
+    # ---- batch 1 and 64 at the start (prompts of 512 tokens), the middle and the end of the context,
+    # each with the fraction of the memory rate it reaches
     points = {}
     if not args.skip_points:
         for b in (1, 64):
-            pms, _, _ = decode_run(b, 512 + K + W, K, W)
-            points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
-        pms, _, _ = decode_run(B, 512 + K + W, K, W)
+            for ctx_end, name in ((512 + K + W, f"decode_b{b}"), (CONTEXT // 2, f"decode_b{b}_ctx{CONTEXT // 2}"),
+                                  (CONTEXT, f"decode_b{b}_ctx{CONTEXT}")):
+                pms, _ = decode_run(eng, b, ctx_end, K, W)
+                points[name] = round(b / pms * 1e3, 1)
+                points[name + "_hbm_frac"] = round(hbm_frac(fig, b, ctx_end, K, pms)[1], 4)
+        pms, _ = decode_run(eng, B, 512 + K + W, K, W)
         points[f"decode_b{B}_ctx512"] = round(B / pms * 1e3, 1)
+        points[f"decode_b{B}_ctx512_hbm_frac"] = round(hbm_frac(fig, B, 512 + K + W, K, pms)[1], 4)
         points["ctx_of_b1_b64"] = 512
+        # ---- what the reference arm measures (`--impl reference`): one sequence at context 512 of a model
+        # with the same layer sizes and REF_LIKE_LAYERS layers, in bfloat16 and in float32
+        del model, eng
+        torch.cuda.empty_cache()
+        like = dict(cfgd, num_hidden_layers=REF_LIKE_LAYERS)
+        like_fig = model_figures(like, REF_LIKE_LAYERS)
+        for dtype, tag in (("bfloat16", "bf16"), ("float32", "f32")):
+            m2 = Model(ModelConfig(compt_type=dtype, nr_ctx=1024, max_tokens=1024, max_batch=1))
+            m2.load_random(config_from_dict(like), seed=0)
+            pms, _ = decode_run(m2.engine, 1, 512 + K + W, K, W)
+            points[f"ref_like_b1_ctx512_{tag}"] = round(1 / pms * 1e3, 1)
+            del m2
+            torch.cuda.empty_cache()
+        points["ref_like_layers"] = REF_LIKE_LAYERS
+    sampler.__exit__()
+    clocks = sampler.summary()
 
     line = {
         "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048-token prompt",

@@ -183,7 +183,15 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_acc
     const int h = blockIdx.x, t = blockIdx.y, c = threadIdx.x;
     const int p = token_pos[t];
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-    const int cfirst = lo / chunk_keys, clast = p / chunk_keys;
+    const int cfirst = lo / chunk_keys;
+    int clast = p / chunk_keys;
+    if (clast >= n_chunks) {
+        // a position beyond what the caller sized the partial results for (token_pos < max_len is the
+        // contract): the keys behind chunk n_chunks - 1 were never looked at, so the row is marked
+        // as not a number instead of read from another head's partial results
+        out[((size_t)t * nh + h) * D + c] = __float2bfloat16_rn(NAN);
+        return;
+    }
     const size_t o = ((size_t)t * nh + h) * n_chunks;
     float M = -INFINITY;
     for (int ch = cfirst; ch <= clast; ch++) M = fmaxf(M, part_ml[(o + ch) * 2]);
@@ -218,7 +226,11 @@ extern "C" int illm_attention_decode(const void* q, int q_stride, const void* kc
                                      int T, int nh, int nkv, int d, int page_size, int window,
                                      float scale, int n_chunks, void* stream) {
     if (T <= 0) return 0;
-    if (nkv <= 0 || nh % nkv || page_size % AD_U || T > 65535 || nkv > 65535) return ILLM_ERR_BAD_ARG;
+    if (nkv <= 0 || nh % nkv || page_size % AD_U || T > 65535 || nkv > 65535 || d <= 0 || n_chunks <= 0)
+        return ILLM_ERR_BAD_ARG;
+    // the kernel reads q, the pages and writes out 16 bytes at a time
+    if ((q_stride & 7) || ((uintptr_t)q & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) || ((uintptr_t)out & 15))
+        return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     const int g = nh / nkv;
 #define AD_CASE(DD, GG)                                                                            \

@@ -254,7 +254,7 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
             for (int i = 0; i < n_my && alive; i++) {
                 const int s = i % STAGES;
                 if (i >= STAGES) {
-                    alive = mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, err);
+                    alive = mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, err, TC_ERR_TIMEOUT_DECODE);
                     if (!alive) break;
                 }
                 const int key0 = (tile_lo + split + i * n_splits) * RD_BN;
@@ -304,13 +304,13 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
     for (int i = 0; i < n_my && alive; i++) {
         const int s = i % STAGES;
         // lanes leave the polling loop one by one: together again before the warp-wide instructions
-        alive = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, (i / STAGES) & 1, err));
+        alive = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, (i / STAGES) & 1, err, TC_ERR_TIMEOUT_DECODE));
         if (!alive) break;
         const int key0 = (tile_lo + split + i * n_splits) * RD_BN + warp * 16;
         if (new_row_here && i == n_my - 1 && warp == ((p & (RD_BN - 1)) >> 4)) {
             // the tile came from the cache before the row of position p was there (or while it was
             // being written): this warp, the only reader of that row, puts in what the helper warp made
-            alive = __all_sync(0xffffffffu, mbar_wait(row_ready, 0, err));
+            alive = __all_sync(0xffffffffu, mbar_wait(row_ready, 0, err, TC_ERR_TIMEOUT_DECODE));
             if (lane < 2 * CH) {
                 const int c = lane < CH ? lane : lane - CH;
                 unsigned char* tile = gbase + (size_t)s * 2 * TILE_BYTES + (lane < CH ? 0 : TILE_BYTES);

@@ -104,11 +104,15 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
         for (int i = tid; i < FA_BN * CH; i += FA_THREADS) {
             const int r = i / CH, c = i % CH;
             const int key = jb * FA_BN + r;
-            const bool ok = key <= last_pos;
+            // keys below the window of the tile's first row are seen by no row of the tile, and the
+            // pages that held them may have gone back to the pool already (table entry -1): such rows
+            // are zero-filled instead of read, so masked scores meet zeros in V, never stale data
+            bool ok = key <= last_pos && key >= lo_key;
             size_t off = 0;
             if (ok) {
                 const int page = bt[key / page_size];
-                off = (((size_t)page * nkv + hk) * page_size + (key % page_size)) * D + c * 8;
+                ok = page >= 0;
+                if (ok) off = (((size_t)page * nkv + hk) * page_size + (key % page_size)) * D + c * 8;
             }
             cp_async_16(smem_u32(kd + swz<D>(r, c)), kc + off, ok ? 16 : 0);
             cp_async_16(smem_u32(vd + swz<D>(r, c)), vc + off, ok ? 16 : 0);

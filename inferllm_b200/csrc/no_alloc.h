@@ -16,7 +16,10 @@
 //
 // Arguments are those of illm_attention_decode (bfloat16 q, cache pages and out; int32 tables),
 // without the two scratch pointers; `max_len` bounds the sequence lengths of the call and decides
-// how much scratch it needs: T * nh * ceil(max_len / 256) * (d + 2) floats.
+// how much scratch it needs: T * nh * ceil(max_len / 256) * (d + 2) floats.  Every token_pos must be
+// below max_len: a token at or beyond it gets a row of NaN instead of a result.  q, the cache pages
+// and out must start on 16-byte boundaries and q_stride must be a multiple of 8 elements, else the
+// call is refused with ILLM_ERR_BAD_ARG.
 //
 // The scratch is one array in the library's device image, ILLM_STATIC_SCRATCH_BYTES (32 MiB)
 // large and 256-byte aligned.  Every GPU on which this library is loaded holds those 32 MiB until

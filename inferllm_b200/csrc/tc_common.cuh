@@ -9,7 +9,12 @@
 #define TC_BK 64
 #define TC_THREADS 192
 #define TC_WAIT_CLOCKS (1LL << 31)
-#define TC_ERR_TIMEOUT 4
+// Error words of the kernels that wait on mbarriers (one word per device, read by the host after a
+// step): which family of kernels gave up a wait.
+#define TC_ERR_TIMEOUT 4            // matrix product (gemm_tc.cu, gemm_tc2.cu)
+#define TC_ERR_TIMEOUT_PREFILL 5    // prompt attention (attention_prefill_tc.cu)
+#define TC_ERR_MISALIGNED_SMEM 6    // a kernel found its shared memory not 1024-byte aligned and did not run
+#define TC_ERR_TIMEOUT_DECODE 7     // decode attention (attention_decode_ring.cu)
 
 __device__ __forceinline__ unsigned tc_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -32,13 +37,14 @@ __device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* err) {
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* err, int code = TC_ERR_TIMEOUT,
+                                          long long limit_clocks = TC_WAIT_CLOCKS) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     do {
         if (mbar_try(bar, parity)) return true;
-    } while (clock64() - t0 < TC_WAIT_CLOCKS);
-    atomicExch(err, TC_ERR_TIMEOUT);
+    } while (clock64() - t0 < limit_clocks);
+    atomicExch(err, code);
     return false;
 }
 __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {

@@ -45,6 +45,7 @@ class Model:
         self.engine: Optional[Engine] = None
         self.sampling = SamplingParams()
         self.end_token: Optional[int] = None
+        self.end_tokens: List[int] = []
         self._slot: Optional[int] = None
         self._history: List[int] = []
         self._n_generated = 0
@@ -63,12 +64,18 @@ class Model:
     def load(self, model_path: str) -> None:
         """Load config.json and the safetensors weights of a model folder."""
         self.engine = Engine.from_folder(model_path, self._options(), self.model_name)
-        self.end_token = self.engine.model.spec.eos_token_ids[0] if self.engine.model.spec.eos_token_ids else None
+        self._take_end_tokens()
 
     def load_random(self, config, seed: int = 0) -> None:
         """Random weights for a typed configuration, made on the device."""
         self.engine = Engine.from_config(config, self._options(), seed)
-        self.end_token = self.engine.model.spec.eos_token_ids[0] if self.engine.model.spec.eos_token_ids else None
+        self._take_end_tokens()
+
+    def _take_end_tokens(self) -> None:
+        """The configuration's end tokens: `end_token` is the first (the single number the
+        reference's `init` takes), `end_tokens` all of them (config.json may list several)."""
+        self.end_tokens = [int(t) for t in self.engine.model.spec.eos_token_ids]
+        self.end_token = self.end_tokens[0] if self.end_tokens else None
 
     def init(self, top_k: int, top_p: float, temp: float, repeat_penalty: float,
              repeat_last_n: int, seed: int, end_token: int) -> None:
@@ -147,9 +154,15 @@ class Model:
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 128,
                  stop_ids: Optional[Sequence[int]] = None, on_token=None) -> GenerationResult:
-        """Generate for many requests; stop ids default to `end_token`."""
+        """Generate for many requests.  `stop_ids` default to the end token given to `init`; where
+        that is one of the configuration's end tokens (or `init` was given none), to all of them:
+        the reference ends a turn on its one end token (application/llama/llama.cpp:237), a
+        config.json may name several."""
         if stop_ids is None:
-            stop_ids = [] if self.end_token is None else [self.end_token]
+            if self.end_token is None or self.end_token in self.end_tokens:
+                stop_ids = list(self.end_tokens)
+            else:
+                stop_ids = [self.end_token]
         sampler = Sampler(self.sampling)
         # the loop that keeps the host one step behind the device; the sampler keeps the windows of
         # last tokens for the repetition penalty on the device

@@ -440,9 +440,15 @@ class Engine:
         """Read the kernels' error word (synchronises)."""
         code = int(self.err.item())
         tc = ops.tc_error_word(self.rt.device)
-        if int(tc.item()):
+        tc_code = int(tc.item())
+        if tc_code:
             tc.zero_()
-            raise EngineError("a wait inside the tensor-core matrix product timed out")
+            family = {4: "a wait inside the tensor-core matrix product (gemm_tc, gemm_tc2) timed out",
+                      5: "a wait inside the tensor-core prompt attention (attention_prefill_tc) timed out",
+                      6: "a tensor-core kernel found its shared memory misaligned and did not run",
+                      7: "a wait inside the decode attention (attention_decode_ring) timed out"}
+            raise EngineError(family.get(tc_code, f"a tensor-core kernel reported error {tc_code}")
+                              + ": the step's results are not valid")
         if code:
             self.err.zero_()
             what = {1: "a token id outside the embedding table", 2: "a cache write to a page that "

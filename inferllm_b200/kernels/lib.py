@@ -43,6 +43,9 @@ _SIGNATURES = {
     "illm_argmax": [P, I, I, I, P, P, P, P],
     "illm_sample": [P, I, I, I, P, P, I, F, F, I, F, P, P, P, P],
     "illm_sample_scratch_elems": [I, I, I, F],
+    "illm_fill_random": [P, I, LL, ctypes.c_ulonglong, F, F, P],
+    "illm_poison_pages": [P, P, LL, I, LL, P, I, P],
+    "illm_selftest_wait_timeout": [P, P, LL, I, P],
 }
 
 

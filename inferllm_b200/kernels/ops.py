@@ -720,3 +720,35 @@ def sample(logits, uniforms, temp, top_k=0, top_p=1.0, repeat_penalty=1.0, last_
                                   float(repeat_penalty), int(top_k), float(top_p), _ptr(uniforms[b0:b1]),
                                   _ptr(out[b0:b1]), _ptr(scratch), _stream()), "sample")
     return out
+
+
+def fill_random(out, key: int, std: float, mean: float = 0.0):
+    """out[i] = mean + std * z_i, z_i value i of the stream `key` (`weights.random_init.random_key`);
+    float32 or bfloat16, in place."""
+    _need(out, "out")
+    _check(load().illm_fill_random(_ptr(out), act_code(out.dtype), out.numel(), int(key), float(std), float(mean),
+                                   _stream()), "fill_random")
+    return out
+
+
+def poison_pages(k, v, pages):
+    """Fill the given pages (int32 tensor on the device) of the cache tensors k, v
+    [entries, pages, kv heads, page_size, head_dim] with NaN, in every entry."""
+    _need(k, "k", None, 5)
+    _need(v, "v", k.dtype, 5)
+    _need(pages, "pages", torch.int32, 1)
+    page_bytes = k.shape[2] * k.shape[3] * k.shape[4] * k.element_size()
+    _check(load().illm_poison_pages(_ptr(k), _ptr(v), k.shape[1] * page_bytes, k.shape[0], page_bytes, _ptr(pages),
+                                    pages.numel(), _stream()), "poison_pages")
+
+
+def selftest_wait_timeout(device, limit_clocks: int = 1 << 20, code: int = 4):
+    """Runs the bounded mbarrier wait of the tensor-core kernels on a barrier nobody arrives at, with
+    a short limit.  Returns (error word, 1 if the wait reported its time-out, clocks waited); the
+    error word is the device's `tc_error_word`, which is left set for `Engine.check_device_errors`."""
+    err = tc_error_word(device)
+    result = torch.zeros(2, dtype=torch.int64, device=device)
+    _check(load().illm_selftest_wait_timeout(_ptr(err), _ptr(result), int(limit_clocks), int(code), _stream()),
+           "selftest_wait_timeout")
+    r = result.tolist()
+    return int(err.item()), int(r[0]), int(r[1])

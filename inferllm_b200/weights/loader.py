@@ -14,13 +14,13 @@ that owns them.
 """
 from __future__ import annotations
 
-import hashlib
 import json
 import os
 from typing import Dict
 
 import torch
 
+from .random_init import random_key, random_values, to_bfloat16_bits
 from .safetensors_io import SafetensorsError, open_model_files, write_safetensors
 
 
@@ -84,22 +84,29 @@ def load_model_weights(model, folder: str) -> None:
 # ---- random weights
 
 
-def _tensor_seed(seed: int, name: str) -> int:
-    h = hashlib.sha256(f"{seed}:{name}".encode()).digest()
-    return int.from_bytes(h[:8], "little") & 0x7FFFFFFFFFFFFFFF
-
-
 def random_tensor(name: str, decl, seed: int, dtype: torch.dtype, device="cpu") -> torch.Tensor:
-    """Matrices N(0, 0.02), norm weights 1 + N(0, 0.02), each from a generator seeded by
-    (seed, tensor name), so a tensor does not depend on which others exist."""
-    gen = torch.Generator(device=device)
-    gen.manual_seed(_tensor_seed(seed, name))
+    """Matrices N(0, 0.02), norm weights 1 + N(0, 0.02), each from the stream of (seed, tensor
+    name), so a tensor does not depend on which others exist.  The numbers are defined bit by bit
+    (`weights.random_init`, `csrc/random_init.h`): on a CUDA device they are made by the fill kernel,
+    on the host by numpy, and both give the same tensor."""
     if decl.init == "int":
         return torch.zeros(decl.shape, dtype=torch.int32, device=device)
-    t = torch.empty(decl.shape, dtype=torch.float32, device=device).normal_(0.0, 0.02, generator=gen)
-    if decl.init == "norm":
-        t += 1.0
-    return t.to(dtype)
+    n = 1
+    for d in decl.shape:
+        n *= int(d)
+    mean = 1.0 if decl.init == "norm" else 0.0
+    if torch.device(device).type == "cuda":
+        from ..kernels import ops
+        store = dtype if dtype in (torch.float32, torch.bfloat16) else torch.float32
+        out = torch.empty(decl.shape, dtype=store, device=device)
+        ops.fill_random(out, random_key(seed, name), 0.02, mean)
+        return out.to(dtype)
+    vals = random_values(seed, name, n, 0.02, mean)
+    if dtype == torch.bfloat16:
+        t = torch.from_numpy(to_bfloat16_bits(vals).view("int16")).view(torch.bfloat16)
+    else:
+        t = torch.from_numpy(vals).to(dtype)
+    return t.reshape(decl.shape)
 
 
 def write_random_model(config, folder: str, seed: int, dtype: torch.dtype = torch.bfloat16) -> str:

@@ -7,7 +7,9 @@
 # 2. writes a tiny random LLaMA (golden_model/: config.json + float32 model.safetensors) with
 #    inferllm_b200's random-weights writer, and the same weights in the reference's .bin container;
 # 3. runs ref_harness on golden_tokens.txt and stores its logits in golden_logits.f32.
-# tests/test_golden.py then compares the plain implementation (tests/plain_llama.py) with those
+# 4. runs ref_ops_harness, which calls the reference's grouped-head attention loops directly, and
+#    stores their inputs and results in golden_gqa_ops.f32.
+# tests/test_plain_and_golden.py then compares the plain implementation (tests/plain_llama.py) with those
 # logits; it needs neither the reference nor a compiler.
 set -e
 REF=${1:?reference source directory}
@@ -19,6 +21,9 @@ mkdir -p "$BUILD"
     && make -j8 InferLLM > make.log 2>&1)
 g++ -std=c++11 -O2 -Wno-multichar -I "$REF/src" -I "$REF/include" "$HERE/ref_harness.cpp" \
     "$BUILD/libInferLLM.a" -lpthread -o "$BUILD/ref_harness"
+g++ -std=c++11 -O2 -Wno-multichar -I "$REF/src" -I "$REF/include" "$HERE/ref_ops_harness.cpp" \
+    "$BUILD/libInferLLM.a" -lpthread -o "$BUILD/ref_ops_harness"
+"$BUILD/ref_ops_harness" "$HERE/golden_gqa_ops.f32"
 cd "$ROOT"
 python - <<PY
 import json, torch, numpy as np

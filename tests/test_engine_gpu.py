@@ -410,6 +410,74 @@ def test_random_batches_against_float32():
         eng.cache.check()
 
 
+@pytest.mark.parametrize("B", [17, 33, 64, 80])
+def test_decode_steps_of_many_sequences(B, tmp_path):
+    """One-token steps of 17, 33, 64 and 80 sequences: from 17 tokens on a decode step takes the
+    library's products (finished tensors instead of K slices into the norms and into the fused
+    attention kernel), and each batch size captures a graph of its own.  Every sequence has another
+    length; all of them are checked against the float32 engine at every decoded position, and two
+    of them (the shortest and the longest) against the plain implementation."""
+    import plain_llama
+
+    from inferllm_b200 import config_from_dict, write_random_model
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=64, intermediate_size=704, vocab_size=640, rope_theta=10000.0,
+               rms_norm_eps=1e-5, max_position_embeddings=512, tie_word_embeddings=False, eos_token_id=2)
+    folder = str(tmp_path)
+    write_random_model(config_from_dict(cfg), folder, 5, torch.bfloat16)
+    rng = np.random.default_rng(B)
+    lens = [int(rng.integers(3, 200)) for _ in range(B)]
+    lens[0], lens[1] = 3, 260
+    n_dec = 6
+    reqs = [rng.integers(0, 640, size=n + n_dec).tolist() for n in lens]
+    eng = make_engine(folder, "bfloat16", max_tokens=B * 320 + 64, max_batch=B)
+    ref = make_engine(folder, "float32", max_tokens=B * 320 + 64, max_batch=B)
+    got = in_batches(eng, reqs, lens, [list(range(B))])
+    want = in_batches(ref, reqs, lens, [list(range(B))])
+    for r in range(B):
+        assert_close(got[r][lens[r] - 1:], want[r][lens[r] - 1:], "bfloat16", f"request {r} of {B}")
+    pcfg, pw = plain_llama.load_weights(folder)
+    for r in (0, 1):
+        plain = plain_llama.forward(pcfg, pw, reqs[r])
+        assert_close(want[r], plain, "float32", f"request {r} of {B}, float32")
+        assert_close(got[r], plain, "bfloat16", f"request {r} of {B}, bfloat16")
+    eng.check_device_errors()
+    eng.cache.check()
+
+
+def test_batch_that_shrinks_across_the_kernel_switch(tmp_path):
+    """Twenty sequences of which eight end early, one per step, so that the live count falls from 20
+    to 12 while decoding: the step changes from the library's products to the package's split
+    product at 16 tokens, and every count replays or captures another graph.  All positions against
+    the float32 engine, the last request to end against the plain implementation."""
+    import plain_llama
+
+    from inferllm_b200 import config_from_dict, write_random_model
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=4, head_dim=64, intermediate_size=704, vocab_size=640, rope_theta=10000.0,
+               rms_norm_eps=1e-5, max_position_embeddings=512, tie_word_embeddings=True, eos_token_id=2)
+    folder = str(tmp_path)
+    write_random_model(config_from_dict(cfg), folder, 6, torch.bfloat16)
+    rng = np.random.default_rng(3)
+    B = 20
+    lens = [int(rng.integers(5, 150)) for _ in range(B)]
+    extra = [2 + i for i in range(8)] + [14] * 12        # requests 0..7 end after 2..9 single-token steps
+    reqs = [rng.integers(0, 640, size=n + e).tolist() for n, e in zip(lens, extra)]
+    eng = make_engine(folder, "bfloat16", max_tokens=B * 192 + 64, max_batch=B)
+    ref = make_engine(folder, "float32", max_tokens=B * 192 + 64, max_batch=B)
+    for _ in range(2):                                   # the second round replays the graphs the first captured
+        got = in_batches(eng, reqs, lens, [list(range(B))])
+        want = in_batches(ref, reqs, lens, [list(range(B))])
+        for r in range(B):
+            assert_close(got[r][lens[r] - 1:], want[r][lens[r] - 1:], "bfloat16", f"request {r}")
+    pcfg, pw = plain_llama.load_weights(folder)
+    plain = plain_llama.forward(pcfg, pw, reqs[19])
+    assert_close(want[19], plain, "float32", "request 19, float32")
+    assert_close(got[19], plain, "bfloat16", "request 19, bfloat16")
+    eng.check_device_errors()
+    eng.cache.check()
+
+
 def test_cache_sized_from_the_memory_that_is_left(model_folders):
     """max_tokens=None: the cache takes `mem_fraction` of what the device has free beside the weights."""
     import gc
@@ -427,3 +495,16 @@ def test_cache_sized_from_the_memory_that_is_left(model_folders):
     assert 0.03 * free <= held <= 0.05 * total
     ids = random_prompt("A", 40, 1)
     assert whole(eng, ids).shape[0] == 40
+
+
+def test_device_errors_name_the_kernel_family(model_folders):
+    """A wait that runs out inside a kernel leaves a code in the device's error word;
+    `check_device_errors` turns it into an error that says which family of kernels gave up, and
+    clears it."""
+    from inferllm_b200.kernels import ops
+    eng = make_engine(model_folders["A"], "bfloat16")
+    for code, words in ((4, "matrix product"), (5, "prompt attention"), (7, "decode attention")):
+        ops.selftest_wait_timeout(torch.device("cuda"), 1 << 18, code)
+        with pytest.raises(EngineError, match=words):
+            eng.check_device_errors()
+        eng.check_device_errors()

@@ -177,3 +177,34 @@ def test_command_line(model_folders, plain_models, tmp_path):
                        capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr
     assert len([ln for ln in r.stdout.splitlines() if ln.startswith("[")]) == 2
+
+
+def test_every_end_token_of_the_configuration_stops_by_default(model_folders, plain_models, tmp_path):
+    """config.json may list several end tokens (tiny B has two); without `stop_ids` generation
+    stops at any of them, through `Model.generate` and through the command line.  The second of two
+    end tokens is made the one that the greedy continuation meets."""
+    import shutil
+    name = "B"
+    cfg, w = plain_models[name]
+    prompt = random_prompt(name, 9, 5)
+    free = plain.greedy_generate(cfg, w, prompt, 10)
+    stop_at = next(i for i in range(2, 10) if free[i] not in free[:i])
+    unused = next(t for t in range(TINY[name]["vocab_size"]) if t not in free)
+    folder = str(tmp_path / "model")
+    shutil.copytree(model_folders[name], folder)
+    with open(os.path.join(folder, "config.json")) as f:
+        c = json.load(f)
+    c["eos_token_id"] = [unused, free[stop_at]]
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(c, f)
+    m = load(folder, "float32", nr_ctx=128, max_tokens=256)
+    assert m.end_token == unused and m.end_tokens == [unused, free[stop_at]]
+    m.init(0, 1.0, 0.0, 1.0, 0, 0, m.end_token)
+    res = m.generate([prompt], max_new_tokens=10)
+    assert res.tokens == [free[:stop_at + 1]] and res.finish == ["stop"]
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llama"), "-m", folder, "-d", "float32", "-c", "128",
+                        "-n", "10", "--temp", "0", "--top_k", "0", "--top_p", "1", "--repeat_penalty", "1", "-s", "1",
+                        "--prompt-ids", ",".join(map(str, prompt))], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    line = [ln for ln in r.stdout.splitlines() if ln.startswith("[0]")][0]
+    assert line == "[0] stop: " + ",".join(map(str, free[:stop_at + 1]))

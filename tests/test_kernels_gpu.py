@@ -621,6 +621,16 @@ def test_attention_decode_ring_with_the_position_encoding_inside(nh, nkv, d, pag
     q1 = ops.rope_kv_write(src, table, rot, pos, seq, dev(pc.table), kc1, vc1, nh, nkv, d, page, True, err_word())
     want = ops.attention_decode_ring(q1, kc1, vc1, dev(pc.table), pos, seq, nh, nkv, d, page, window, scale, 4096)
     assert np.isfinite(f64(want)).all()
+    # the plain implementation of the same: rotation of Q and of the new K row, the new row put behind
+    # the sequence's cached keys and values, attention of the one query at the last position
+    x = f64(qkv_bf16).reshape(T, nh + 2 * nkv, d)
+    rotated = plain.rope_rotate_half(x[:, :nh + nkv], pos.cpu().numpy(), 1e4, rot_dim=rot) if rot else x[:, :nh + nkv]
+    plain_rows = []
+    for b in range(T):
+        k, v = f64(pc.k[b]).copy(), f64(pc.v[b]).copy()
+        k[-1], v[-1] = rotated[b, nh:], x[b, nh + nkv:]
+        plain_rows.append(plain_attention_rows(rotated[b:b + 1, :nh], k, v, [lens[b] - 1], nh, nkv, scale, window))
+    plain_rows = np.concatenate(plain_rows).reshape(T, nh * d)
     for splits in (None, 1, 2, 5, 16):
         kc2, vc2 = dev(pc.kc), dev(pc.vc)
         e = err_word()
@@ -632,6 +642,7 @@ def test_attention_decode_ring_with_the_position_encoding_inside(nh, nkv, d, pag
             assert torch.equal(kc2[pg, :, off], kc1[pg, :, off]) and torch.equal(vc2[pg, :, off], vc1[pg, :, off]), \
                 f"cache row of sequence {b}, {splits} splits"
         assert maxrel(f64(got), f64(want)) <= 2 ** -9, f"{splits} splits"
+        assert maxrel(f64(got), plain_rows) <= 2 ** -7, f"{splits} splits, against the plain implementation"
     # a layer that reads another layer's cache entry: nothing is written
     kc3, vc3 = kc1.clone(), vc1.clone()
     got = ops.attention_decode_ring(part if slices else qkv_bf16, kc3, vc3, dev(pc.table), pos, seq, nh, nkv, d, page,
@@ -858,3 +869,53 @@ def test_sample_large_vocabulary_and_greedy_limit():
     assert out.tolist() == lg.argmax(-1).tolist()     # top_k = 1 is greedy
     out = ops.sample(dev(lg), dev(u), 0.05, 0, 0.3, 1.0, None).cpu()
     assert out[2] == 77777
+
+
+# ---- utilities: random weights, poisoned pages, the bounded wait
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n,std,mean", [(1, 0.02, 0.0), (1000, 0.02, 1.0), (300007, 0.5, 0.0)])
+def test_fill_random_is_the_numpy_twin_bit_for_bit(dtype, n, std, mean):
+    from inferllm_b200.weights.random_init import random_key, random_values, to_bfloat16_bits
+    key = random_key(7, "model.layers.1.mlp.up_proj.weight")
+    out = ops.fill_random(torch.empty(n, dtype=DT[dtype], device="cuda"), key, std, mean).cpu()
+    want = random_values(7, "model.layers.1.mlp.up_proj.weight", n, std, mean)
+    if dtype == "float32":
+        assert np.array_equal(out.numpy().view(np.uint32), want.view(np.uint32))
+    else:
+        assert np.array_equal(out.view(torch.int16).numpy().view(np.uint16), to_bfloat16_bits(want))
+    if n > 1000:
+        z = (want.astype(np.float64) - mean) / std
+        assert abs(z.mean()) < 0.01 and abs(z.std() - 1) < 0.01 and np.abs(z).max() <= 6.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_poison_pages_fills_exactly_the_named_pages(dtype):
+    k = torch.randn(3, 10, 2, 8, 24, device="cuda").to(DT[dtype])
+    v = torch.randn(3, 10, 2, 8, 24, device="cuda").to(DT[dtype])
+    k0, v0 = k.clone(), v.clone()
+    ops.poison_pages(k, v, dev(torch.tensor([7, 0, 3], dtype=torch.int32)))
+    for t, t0 in ((k, k0), (v, v0)):
+        hit = torch.isnan(t).all(dim=(2, 3, 4))
+        assert hit[:, [0, 3, 7]].all() and int(hit.sum()) == 9
+        keep = [1, 2, 4, 5, 6, 8, 9]
+        assert torch.equal(t[:, keep], t0[:, keep])
+
+
+def test_a_wait_that_runs_out_sets_the_error_word_and_the_kernel_returns():
+    """The tensor-core kernels wait on mbarriers through one bounded wait; here it waits, with a
+    short limit, on a barrier at which nothing ever arrives.  The kernel comes back by itself, the
+    wait tells its caller that it gave up, the device's error word names the kernel family, and
+    the device goes on working."""
+    device = torch.device("cuda")
+    word = ops.tc_error_word(device)
+    word.zero_()
+    for code in (4, 5, 7):
+        got, gave_up, clocks = ops.selftest_wait_timeout(device, limit_clocks=1 << 18, code=code)
+        assert (got, gave_up) == (code, 1)
+        assert (1 << 18) <= clocks < (1 << 24)
+        word.zero_()
+    # the context is as usable as before
+    x = torch.arange(8, device="cuda", dtype=torch.float32)
+    assert float((x * 2).sum()) == 56.0

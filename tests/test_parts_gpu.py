@@ -109,6 +109,42 @@ def test_attention_part_prompt_then_tokens(dtype, H, nh, nkv, d, window, theta, 
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_part_window_and_a_later_portion_after_pages_were_released(dtype):
+    """A windowed layer with pages smaller than a key tile of the prompt kernel: after a first
+    portion of 100 tokens the pages below the window have gone back to the pool (their table entries
+    read -1, and other sequences' data lies in them), then a second portion of 30 tokens arrives in
+    one step.  Its first key tile starts below the window, inside the released pages: those keys
+    must be skipped, not read."""
+    H, nh, nkv, d, window, theta = 128, 2, 1, 64, 40, 1e4
+    req = PagedKV(nkv, d, window)
+    h = PartHarness({0: req}, dtype, page_size=16, num_pages=12)
+    att = _attention(h, H, nh, nkv, d, window, theta)
+    ws = {k: randn(*v.shape, seed=i + 1, scale=0.15, dtype=torch.bfloat16) for i, (k, v) in enumerate(att.tensors().items())}
+    att.load({k: v.cuda() for k, v in ws.items()})
+    x = randn(130, H, seed=31, dtype=DT[dtype])
+    ref = plain.self_attention(f64(x), f64(ws["q_proj.weight"]), f64(ws["k_proj.weight"]), f64(ws["v_proj.weight"]),
+                               f64(ws["o_proj.weight"]), np.arange(130), nh, nkv, d, theta, window, None)[0]
+    s = h.cache.alloc_slot()
+    got = []
+    for lo, hi in ((0, 100), (100, 130)):
+        ctx, plan = h.context([s], [hi - lo])
+        got.append(att.forward(x[lo:hi].cuda(), ctx, ctx.cache_view(0), True))
+        h.cache.commit_step(plan)
+        if hi == 100:
+            held = h.cache.paged[0].ledger.pages[s]
+            assert min(held) == 3, "the pages below the window should have been released"
+            # what lies in released pages now is somebody else's: make it loud
+            g = h.cache.paged[0]
+            free = [p for p in range(12) if p not in held.values()]
+            g.k[:, free] = float("nan")
+            g.v[:, free] = float("nan")
+    out = f64(torch.cat(got))
+    assert np.isfinite(out).all()
+    assert rel_err(out, ref) <= TOL[dtype]
+    assert int(h.err.item()) == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_attention_part_reading_another_entrys_cache(dtype):
     """writes=False: the mixer projects only its queries and attends to the keys and values that
     the owner of the cache entry stored in the same step."""

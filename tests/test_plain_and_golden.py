@@ -1,7 +1,8 @@
 """The plain implementation against MegEngine/InferLLM's own compiled code, and against itself
 (no GPU).  tests/golden/golden_logits.f32 was produced by tests/golden/make_golden.sh, which
 builds the reference on the CPU and runs its LLaMA graph (naive kernels) on
-tests/golden/golden_model; this test needs neither the reference nor a compiler."""
+tests/golden/golden_model, and calls its grouped-head attention loops directly
+(tests/golden/golden_gqa_ops.f32); this test needs neither the reference nor a compiler."""
 import os
 
 import numpy as np
@@ -25,6 +26,33 @@ def test_plain_matches_the_compiled_reference():
         assert np.abs(mine - one_by_one).max() <= 2e-6 * scale     # the reference computes in float32
         assert np.abs(mine[-1] - whole_last).max() <= 2e-6 * scale
     assert row == ref.shape[0]
+
+
+def test_plain_grouped_heads_match_the_references_own_loops():
+    """golden_gqa_ops.f32 holds what the reference's grouped-head loops give (6 query heads over 2 KV
+    heads of size 24, 7 cached positions and 5 new tokens): scores with the K head h / (heads per
+    group) (src/kern/naive/naive.cpp:576-604), scale and causal mask (:531-553), softmax (:209-240),
+    weighted values with the V head of the group (:634-662).  The plain functions must agree on the
+    same inputs."""
+    nh, nkv, d, past, n = 6, 2, 24, 7, 5
+    total = past + n
+    blob = np.fromfile(os.path.join(GOLDEN, "golden_gqa_ops.f32"), dtype="<f4").astype(np.float64)
+    sizes = [n * nh * d, total * nkv * d, total * nkv * d, nh * n * total, nh * n * total, nh * n * total, n * nh * d]
+    assert blob.size == sum(sizes)
+    q, k, v, scores, masked, probs, out = np.split(blob, np.cumsum(sizes)[:-1])
+    q, k, v = q.reshape(n, nh, d), k.reshape(total, nkv, d), v.reshape(total, nkv, d)
+    s = plain.attention_scores(q, k, nh, nkv)
+    assert np.abs(s - scores.reshape(nh, n, total)).max() <= 1e-6 * np.abs(s).max()
+    m = plain.scale_and_mask(s, 1.0 / np.sqrt(d), past=past)
+    ref_m = masked.reshape(nh, n, total)
+    assert np.array_equal(np.isneginf(m), np.isneginf(ref_m))
+    assert np.abs(np.where(np.isneginf(m), 0, m) - np.where(np.isneginf(ref_m), 0, ref_m)).max() <= 1e-6
+    p = plain.softmax_rows(m)
+    assert np.abs(p - probs.reshape(nh, n, total)).max() <= 1e-6
+    o = plain.weighted_values(p, v, nh, nkv)
+    assert np.abs(o.reshape(n, nh * d) - out.reshape(n, nh * d)).max() <= 1e-6 * np.abs(o).max()
+    # and the heads really are grouped: head 2 reads K head 0, head 3 reads K head 1
+    assert np.allclose(s[2], q[:, 2] @ k[:, 0].T) and np.allclose(s[3], q[:, 3] @ k[:, 1].T)
 
 
 def test_plain_is_causal_and_prefix_stable(plain_models):

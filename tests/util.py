@@ -8,6 +8,11 @@ import numpy as np
 F32_TOL = 2e-5
 BF16_TOL = 4e-2
 TOL = {"float32": F32_TOL, "bfloat16": BF16_TOL}
+# Beside the largest difference, the mean of |difference| and the mean of the signed difference, both
+# relative to max |reference| (the three figures of the reference's own checker, test/checker.cpp:46-99):
+# a wrong rounding point or a bias shows in the means long before it reaches the bound on the maximum.
+MEAN_TOL = {"float32": 2e-6, "bfloat16": 8e-3}
+BIAS_TOL = {"float32": 5e-7, "bfloat16": 2e-3}
 
 
 def rel_err(got, ref):
@@ -21,6 +26,12 @@ def rel_err(got, ref):
 def assert_close(got, ref, dtype, what=""):
     e = rel_err(got, ref)
     assert e <= TOL[dtype], f"{what}: relative error {e:.3e} exceeds {TOL[dtype]:.1e} ({dtype})"
+    diff = np.asarray(got, np.float64) - np.asarray(ref, np.float64)
+    top = max(np.abs(np.asarray(ref, np.float64)).max(), 1e-30)
+    mean, bias = float(np.abs(diff).mean() / top), float(abs(diff.mean()) / top)
+    assert mean <= MEAN_TOL[dtype], f"{what}: mean |difference| {mean:.3e} exceeds {MEAN_TOL[dtype]:.1e} ({dtype})"
+    if diff.size >= 4096:       # the mean of few numbers is no evidence of a bias
+        assert bias <= BIAS_TOL[dtype], f"{what}: mean difference {bias:.3e} exceeds {BIAS_TOL[dtype]:.1e} ({dtype})"
     return e
 
 
