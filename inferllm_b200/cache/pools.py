@@ -100,20 +100,23 @@ class PageLedger:
     def release_outside_window(self, slot: int, seq_len: int) -> None:
         """After a step: pages whose positions are all older than the next query's window."""
         if self.window is None:
-            return
+            return []
         first_needed_pos = seq_len - self.window + 1  # oldest key the next token may see
         if first_needed_pos <= 0:
-            return
+            return []
         first_page = first_needed_pos // self.page_size
         have = self.pages[slot]
-        gone = [lp for lp in have if lp < first_page]
-        self.pool.free([have.pop(lp) for lp in gone])
+        gone = [have.pop(lp) for lp in [lp for lp in have if lp < first_page]]
+        self.pool.free(gone)
+        return gone
 
     def release_all(self, slot: int) -> None:
         have = self.pages[slot]
-        self.pool.free(list(have.values()))
+        gone = list(have.values())
+        self.pool.free(gone)
         have.clear()
         self.n_logical[slot] = 0
+        return gone
 
     def row(self, slot: int, width: int, out) -> None:
         """Write the slot's logical->physical table into out[0:width] (-1 = no page)."""

@@ -91,9 +91,12 @@ class StepPlan:
 
 class SequenceCache:
     def __init__(self, requests: Dict[int, object], num_slots: int, num_pages: int, page_size: int,
-                 max_seq_len: int, runtime=None):
+                 max_seq_len: int, runtime=None, poison_freed_pages: bool = False):
         """`requests`: cache entry number -> PagedKV | FixedState | None.  `runtime=None` keeps
-        the cache host-only (bookkeeping without device storage)."""
+        the cache host-only (bookkeeping without device storage).  `poison_freed_pages`: pages that
+        go back to the pool are filled with NaN on the device, so that a kernel that reads a page
+        its sequence does not hold shows it."""
+        self.poison_freed_pages = bool(poison_freed_pages)
         if num_slots <= 0 or num_pages <= 0 or page_size <= 0:
             raise CacheError("num_slots, num_pages and page_size must be positive")
         self.num_slots, self.num_pages, self.page_size = int(num_slots), int(num_pages), int(page_size)
@@ -158,9 +161,16 @@ class SequenceCache:
         if not self.slots.is_held(slot):
             raise CacheError(f"slot {slot} freed twice (or never handed out)")
         for g in self.paged:
-            g.ledger.release_all(slot)
+            self._poison(g, g.ledger.release_all(slot))
         self.seq_len[slot] = 0
         self.slots.free([slot])
+
+    def _poison(self, group, pages) -> None:
+        if self.poison_freed_pages and pages and group.k is not None:
+            import torch
+
+            from ..kernels import ops
+            ops.poison_pages(group.k, group.v, torch.tensor(sorted(pages), dtype=torch.int32, device=group.k.device))
 
     def reset(self) -> None:
         for slot in range(self.num_slots):
@@ -201,7 +211,7 @@ class SequenceCache:
         for s, q in zip(plan.slots, plan.q_lens):
             self.seq_len[s] += q
             for g in self.paged:
-                g.ledger.release_outside_window(s, self.seq_len[s])
+                self._poison(g, g.ledger.release_outside_window(s, self.seq_len[s]))
 
     # ---- views
 

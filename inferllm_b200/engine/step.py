@@ -47,6 +47,7 @@ class EngineOptions:
     page_size: int = 64
     cuda_graphs: bool = True       # replay one-token-per-sequence steps from captured CUDA graphs
     gemm: str = "auto"             # bfloat16 products: "auto" | "tc" | "library" (see kernels.ops.set_gemm_backend)
+    poison_freed_pages: bool = False    # fill pages that go back to the pool with NaN (a check, not for serving)
 
 
 @dataclass
@@ -143,7 +144,11 @@ class Engine:
         num_pages = max(1, -(-max_tokens // ps))
         num_slots = options.max_batch or num_pages
         self.cache = SequenceCache(self.model.cache_requests(), num_slots, num_pages, ps, max_seq,
-                                   self.rt)
+                                   self.rt, poison_freed_pages=options.poison_freed_pages)
+        if options.poison_freed_pages:          # pages that no sequence has held yet are as foreign as freed ones
+            for g in self.cache.paged:
+                g.k.fill_(float("nan"))
+                g.v.fill_(float("nan"))
         self.err = torch.zeros(1, dtype=torch.int32, device=dev)
         self._stages = [(None, None, None)] * 4    # (pinned tensor, its numpy view, copy-done event)
         self._tok_bufs, self._tok_next = [None] * 4, 0   # pinned buffers for sampled tokens on their way to the host

@@ -140,6 +140,43 @@ def test_unequal_batches_with_slot_reuse(name, dtype, model_folders, plain_logit
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_slot_reuse_with_poisoned_pages(name, dtype, model_folders, plain_logits):
+    """The same batches on an engine that fills every page that goes back to the pool (and every
+    page nobody has held yet) with NaN: a kernel that reads a page its sequence does not hold, or
+    a place of its last page behind its length, gives NaN instead of a plausible number."""
+    maxpos = TINY[name]["max_position_embeddings"]
+    total = [maxpos, 70, 33, 129, 64, 1, 65, 100]
+    prefill = [maxpos - 20, 65, 1, 64, 63, 1, 33, 90]
+    reqs = [random_prompt(name, n, 500 + i) for i, n in enumerate(total)]
+    need = max(sum(-(-total[r] // 64) for r in b) for b in ([0, 1, 2], [3, 4, 5], [6, 7]))
+    eng = make_engine(model_folders[name], dtype, max_tokens=64 * need, max_batch=3, poison=True)
+    got = in_batches(eng, reqs, prefill, [[0, 1, 2], [3, 4, 5], [6, 7]])
+    for r, ids in enumerate(reqs):
+        assert_close(got[r], plain_logits(name, ids), dtype, f"{name} request {r} in batches, poisoned pages")
+    eng.check_device_errors()
+    eng.cache.check()
+    free = [p for p in range(need)]
+    k = eng.cache.paged[0].k
+    assert bool(torch.isnan(k[:, free].float()).all()), "all pages are free again and must be poisoned"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_random_weights_are_the_same_from_a_folder_and_on_the_device(dtype, tmp_path):
+    """One seed gives one model: written to a folder by `write_random_model` (host generator) and read
+    back, or filled on the device by `Engine.from_config` (fill kernel), the tensors are the same
+    bits and so are the logits."""
+    from inferllm_b200 import Engine, EngineOptions, config_from_dict, write_random_model
+    cfg = config_from_dict(TINY["A"])
+    folder = str(tmp_path)
+    write_random_model(cfg, folder, 1234, torch.float32 if dtype == "float32" else torch.bfloat16)
+    a = Engine.from_folder(folder, EngineOptions(dtype=dtype, max_tokens=256))
+    b = Engine.from_config(cfg, EngineOptions(dtype=dtype, max_tokens=256), 1234)
+    ids = random_prompt("A", 50, 3)
+    assert np.array_equal(whole(a, ids), whole(b, ids))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_long_decoding_and_first_tokens(dtype, model_folders, plain_logits):
     """A one-token prompt decoded for hundreds of steps across page borders, next to a second
     sequence that starts at the same time and ends early."""

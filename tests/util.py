@@ -35,11 +35,11 @@ def assert_close(got, ref, dtype, what=""):
     return e
 
 
-def make_engine(folder, dtype, max_tokens=1024, page_size=64, max_batch=None, max_seq_len=None):
+def make_engine(folder, dtype, max_tokens=1024, page_size=64, max_batch=None, max_seq_len=None, poison=False):
     from inferllm_b200 import Engine, EngineOptions
     return Engine.from_folder(folder, EngineOptions(
         dtype=dtype, max_tokens=max_tokens, page_size=page_size, max_batch=max_batch,
-        max_seq_len=max_seq_len))
+        max_seq_len=max_seq_len, poison_freed_pages=poison))
 
 
 class PartHarness:
