@@ -1,0 +1,93 @@
+// One GPU as the engine sees it: a stream, memory, the library's matrix product and the kernels'
+// error words.
+//
+// Memory comes in two kinds.  Persistent blocks (weights, cache pages, tables, inputs and outputs of
+// captured graphs) are taken from the driver one by one and live until they are freed.  Everything a
+// step computes on its way (activations, partial results, scratch of kernels) comes from the step
+// arena: a list of large blocks from which allocations are cut off in order and which is rewound,
+// not freed, when the next step begins.  The same sequence of allocations therefore gets the same
+// addresses every time, which is what lets a step be captured in a CUDA graph and replayed, and no
+// step pays the driver for memory once the arena has seen its size.  The arena only grows: a block
+// is never given back or moved while the device lives, so addresses inside captured graphs stay
+// valid.  The reference's counterpart is its Device with a free-list pool per size
+// (src/core/device.cpp: allocate / free_device) and a workspace that is re-sized when the token
+// count changes (src/core/graph.cpp:169-180).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <string>
+#include <vector>
+
+#include "util/dtype.h"
+#include "util/error.h"
+
+namespace illm {
+
+// Raises KernelError for a non-zero status of a kernel entry point (`what` names it).
+void check_kernel(int code, const char* what);
+// Raises EngineError for a CUDA runtime error.
+void check_cuda(cudaError_t e, const char* what);
+
+class Device {
+public:
+    // `stream`: the stream all work is issued to; nullptr creates one (the Python binding passes the
+    // stream of the framework whose tensors it exchanges).
+    explicit Device(int ordinal, cudaStream_t stream = nullptr);
+    ~Device();
+    Device(const Device&) = delete;
+
+    int ordinal() const { return ordinal_; }
+    int n_sms() const { return n_sms_; }
+    cudaStream_t stream() const { return stream_; }
+    void set_stream(cudaStream_t s);
+    void make_current() const;
+    void synchronize() const;
+    size_t mem_free() const;
+
+    // persistent memory (zeroed when `zero`); `what` goes into the error message when the device is full
+    void* alloc_persistent(size_t bytes, const char* what, bool zero = false);
+    void free_persistent(void* p);
+
+    // the step arena
+    void* alloc(size_t bytes);                 // 256-byte aligned; valid until the arena is rewound
+    template <typename T> T* alloc_n(size_t n) { return (T*)alloc(n * sizeof(T)); }
+    void arena_rewind();                       // a new step begins
+    size_t arena_bytes() const;                // what the arena holds from the driver
+    unsigned long long arena_generation() const { return arena_generation_; }   // grows whenever a block was added
+
+    int* tc_error_word() const { return tc_err_; }       // bounded waits of the tensor-core kernels
+    int* step_error_word() const { return step_err_; }   // ids outside the table, writes to unheld pages, ...
+    // Read and clear both words (synchronises); returns {tensor-core word, step word}.
+    std::pair<int, int> take_error_words();
+
+    // bfloat16 x [M, K] . w [N, K]^T -> out [M, N] (bfloat16 or float32) with float32 accumulation by
+    // the library (cuBLAS), as the reference uses cublasSgemm for its float32 products
+    // (src/kern/gpu/kernel_gpu.cu:420-435).
+    void library_gemm_bf16(const void* x, const void* w, void* out, DType out_dtype, int M, int N, int K);
+
+    // Copy a small host array to the device without making the host wait for the work already queued:
+    // through a ring of pinned staging buffers, each reused only when its copy has left.
+    void upload_small(void* dst, const void* src, size_t bytes);
+
+    // pinned host memory (staging of a step's index arrays and of sampled tokens)
+    void* alloc_pinned(size_t bytes);
+    void free_pinned(void* p);
+
+private:
+    struct Block { char* base; size_t size, used; };
+    int ordinal_, n_sms_ = 148;
+    cudaStream_t stream_ = nullptr;
+    bool own_stream_ = false;
+    std::vector<Block> blocks_;
+    size_t cur_ = 0;
+    unsigned long long arena_generation_ = 0;
+    int *tc_err_ = nullptr, *step_err_ = nullptr;
+    void* cublas_ = nullptr;
+    void* cublas_ws_ = nullptr;
+    struct SmallStage { char* host = nullptr; size_t cap = 0; cudaEvent_t done = nullptr; bool used = false; };
+    SmallStage small_[8];
+    int small_next_ = 0;
+};
+
+}  // namespace illm

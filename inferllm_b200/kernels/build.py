@@ -1,10 +1,14 @@
-"""Compiling the CUDA sources of `inferllm_b200/csrc` into one shared library for sm_100a.
+"""Compiling inferllm_b200 for sm_100a: the CUDA kernels of `csrc/`, the C++ core beside them (one
+shared library, `libinferllm_b200.so`) and the two programs `illm_llama` and `illm_trace_run`.
 
-nvcc is called directly (no torch headers are involved: the entry points are plain C
-functions that take device pointers), so a build from scratch takes well under a minute.
-The library is kept in `csrc/_build/` inside the package when that folder can be written,
-else in a per-user folder under the system's temporary directory; a stamp of the sources
-and flags beside it says whether it is current.  Progress lines go to stderr.
+nvcc compiles the `.cu` files and g++ the `.cpp` files (no framework headers are involved: the
+kernels' entry points are plain C functions that take device pointers, and the core is plain
+C++17 over the CUDA runtime and cuBLAS), so a build from scratch takes about a minute.  The results
+are kept in `csrc/_build/` inside the package when that folder can be written, else in a per-user
+folder under the system's temporary directory; a stamp per object file says whether it is current,
+so a change rebuilds only what it touches.  Progress lines go to stderr.
+
+    python inferllm_b200/kernels/build.py [--force]
 """
 from __future__ import annotations
 
@@ -17,10 +21,14 @@ import tempfile
 import time
 from concurrent.futures import ThreadPoolExecutor
 
-CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
+PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CSRC = os.path.join(PKG, "csrc")
 LIB_NAME = "libinferllm_b200.so"
+PROGRAMS = {"illm_llama": "programs/llama.cpp", "illm_trace_run": "programs/trace_run.cpp"}
+CORE_DIRS = ("util", "config", "weights", "device", "cache", "kernels", "parts", "models", "engine", "sampling", "binding")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+CXX_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-Wall", "-Wno-unused-function", "-ffp-contract=off"]
 
 
 class BuildError(RuntimeError):
@@ -39,18 +47,54 @@ def find_nvcc() -> str:
                      "CUDA kernels of inferllm_b200 cannot be compiled, and there is no other path")
 
 
+def find_cxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++")):
+        if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
+            return cand
+    raise BuildError("no C++ compiler found (looked at $CXX, g++ and c++)")
+
+
+def cuda_home(nvcc: str) -> str:
+    return os.path.dirname(os.path.dirname(os.path.realpath(nvcc)))
+
+
 def sources():
-    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+    """(relative path, kind) of everything that goes into the library."""
+    out = [(os.path.join("csrc", f), "cu") for f in sorted(os.listdir(CSRC)) if f.endswith(".cu")]
+    for d in CORE_DIRS:
+        full = os.path.join(PKG, d)
+        if os.path.isdir(full):
+            out += [(os.path.join(d, f), "cpp") for f in sorted(os.listdir(full)) if f.endswith(".cpp")]
+    return out
+
+
+def _headers_hash() -> str:
+    h = hashlib.sha256()
+    for d in ("csrc", "programs") + CORE_DIRS:
+        full = os.path.join(PKG, d)
+        if not os.path.isdir(full):
+            continue
+        for f in sorted(os.listdir(full)):
+            if f.endswith((".h", ".cuh")):
+                h.update(f"{d}/{f}".encode())
+                with open(os.path.join(full, f), "rb") as fh:
+                    h.update(fh.read())
+    h.update(" ".join(NVCC_FLAGS + CXX_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _source_stamp(rel: str, headers: str) -> str:
+    h = hashlib.sha256(headers.encode())
+    with open(os.path.join(PKG, rel), "rb") as fh:
+        h.update(fh.read())
+    return h.hexdigest()
 
 
 def _stamp() -> str:
-    h = hashlib.sha256()
-    for f in sorted(os.listdir(CSRC)):
-        if f.endswith((".cu", ".cuh", ".h")):
-            h.update(f.encode())
-            with open(os.path.join(CSRC, f), "rb") as fh:
-                h.update(fh.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    headers = _headers_hash()
+    h = hashlib.sha256(headers.encode())
+    for rel, _ in sources() + [(p, "cpp") for p in PROGRAMS.values()]:
+        h.update(_source_stamp(rel, headers).encode())
     return h.hexdigest()
 
 
@@ -77,23 +121,26 @@ def build_dir() -> str:
     alt = os.path.join(tempfile.gettempdir(), f"inferllm_b200_build_{os.getuid()}")
     if _writable_dir(alt):
         return alt
-    raise BuildError(f"no writable folder for the compiled kernels (tried {local} and {alt})")
+    raise BuildError(f"no writable folder for the compiled library (tried {local} and {alt})")
 
 
-def current_library():
-    """Path of an up-to-date library if one exists (in-tree first), else None."""
-    want = _stamp()
+def _candidates():
     cands = [os.path.join(CSRC, "_build"),
              os.path.join(tempfile.gettempdir(), f"inferllm_b200_build_{os.getuid()}")]
     if os.environ.get("ILLM_BUILD_DIR"):
         cands.insert(0, os.environ["ILLM_BUILD_DIR"])
-    for d in cands:
+    return cands
+
+
+def current_library():
+    """Path of an up-to-date library (with its programs beside it) if one exists, in-tree first."""
+    want = _stamp()
+    for d in _candidates():
         lib, st = os.path.join(d, LIB_NAME), os.path.join(d, "stamp.txt")
-        if os.path.isfile(lib) and os.path.isfile(st):
+        if os.path.isfile(lib) and os.path.isfile(st) and all(os.path.isfile(os.path.join(d, p)) for p in PROGRAMS):
             with open(st) as f:
-                have = f.read().strip()
-            if have == want:
-                return lib
+                if f.read().strip() == want:
+                    return lib
     return None
 
 
@@ -103,39 +150,73 @@ def build(force: bool = False, verbose: bool = True, extra_flags=()) -> str:
         lib = current_library()
         if lib:
             return lib
-    nvcc = find_nvcc()
+    nvcc, cxx = find_nvcc(), find_cxx()
+    inc = os.path.join(cuda_home(nvcc), "include")
     out = build_dir()
-    stamp = _stamp()
+    headers = _headers_hash()
     srcs = sources()
-    if verbose:
-        _log(f"compiling {len(srcs)} CUDA sources for sm_100a into {out} (first call only)")
     t0 = time.time()
+    todo = []
+    for rel, kind in srcs:
+        obj = os.path.join(out, rel.replace(os.sep, "_").rsplit(".", 1)[0] + ".o")
+        stamp = _source_stamp(rel, headers) + " " + " ".join(extra_flags)
+        st_path = obj + ".stamp"
+        fresh = False
+        if not force and os.path.isfile(obj) and os.path.isfile(st_path):
+            with open(st_path) as f:
+                fresh = f.read() == stamp
+        todo.append((rel, kind, obj, stamp, fresh))
+    stale = [t for t in todo if not t[4]]
+    if verbose and stale:
+        _log(f"compiling {len(stale)} of {len(todo)} sources for sm_100a into {out} (first call only)")
 
-    def compile_one(src):
-        obj = os.path.join(out, src[:-3] + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, *extra_flags, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
+    def compile_one(item):
+        rel, kind, obj, stamp, fresh = item
+        if fresh:
+            return obj
+        src = os.path.join(PKG, rel)
+        if kind == "cu":
+            cmd = [nvcc, *NVCC_FLAGS, *extra_flags, "-I", CSRC, "-I", PKG, "-c", src, "-o", obj]
+        else:
+            cmd = [cxx, *CXX_FLAGS, "-I", PKG, "-I", inc, "-c", src, "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
-            raise BuildError(f"nvcc failed on {src}:\n{r.stdout}\n{r.stderr}")
+            raise BuildError(f"compiling {rel} failed:\n{r.stdout}\n{r.stderr}")
+        with open(obj + ".stamp", "w") as f:
+            f.write(stamp)
         if verbose:
-            _log(f"  compiled {src} ({time.time() - t0:.0f} s)")
+            _log(f"  compiled {rel} ({time.time() - t0:.0f} s)")
         if r.stderr.strip() and verbose and "-Xptxas" in " ".join(extra_flags):
             _log(r.stderr)
         return obj
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as pool:
-        objs = list(pool.map(compile_one, srcs))
+        objs = list(pool.map(compile_one, todo))
     lib = os.path.join(out, LIB_NAME)
     tmp = lib + f".tmp{os.getpid()}"
-    r = subprocess.run([nvcc, "-shared", "-o", tmp, *objs], capture_output=True, text=True)
+    r = subprocess.run([nvcc, "-shared", "-o", tmp, *objs, "-lcublas"], capture_output=True, text=True)
     if r.returncode != 0:
         raise BuildError(f"link failed:\n{r.stdout}\n{r.stderr}")
     os.replace(tmp, lib)
+    for prog, rel in PROGRAMS.items():
+        exe = os.path.join(out, prog)
+        tmp = exe + f".tmp{os.getpid()}"
+        cmd = [cxx, *CXX_FLAGS, "-I", PKG, "-I", inc, os.path.join(PKG, rel), "-o", tmp, f"-L{out}", "-linferllm_b200",
+               "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(cuda_home(nvcc), "lib64")]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise BuildError(f"building {prog} failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, exe)
     with open(os.path.join(out, "stamp.txt"), "w") as f:
-        f.write(stamp + "\n")
+        f.write(_stamp() + "\n")
     if verbose:
-        _log(f"built {lib} in {time.time() - t0:.0f} s")
+        _log(f"built {lib} and {', '.join(PROGRAMS)} in {time.time() - t0:.0f} s")
     return lib
+
+
+def program(name: str) -> str:
+    """Path of a built program (`illm_llama`, `illm_trace_run`), building first if anything is stale."""
+    return os.path.join(os.path.dirname(build()), name)
 
 
 if __name__ == "__main__":
