@@ -286,9 +286,8 @@ def run_scenario(args, cfg, cfgd, model_name, L, fig, pk, pk_src):
     prompts = [torch.randint(0, cfgd["vocab_size"], (n,), generator=g).tolist() for n in lens]
     ctx = max(lens) + new + 1
     max_tokens = sum(-(-(n + new + 1) // 64) * 64 for n in lens) + 64
-    model = Model(ModelConfig(compt_type="bfloat16", nr_ctx=ctx, max_tokens=max_tokens, max_batch=B))
+    model = Model(ModelConfig(compt_type="bfloat16", nr_ctx=ctx, max_tokens=max_tokens, max_batch=B, gemm=args.gemm))
     model.load_random(cfg, seed=0)
-    ops.set_gemm_backend(args.gemm)
     model.init(top_k=0, top_p=1.0, temp=0.0, repeat_penalty=1.0, repeat_last_n=0, seed=0, end_token=-1)
     model.generate([p[:64] for p in prompts], max_new_tokens=4, stop_ids=[])       # compile, capture
     with ClockSampler() as cs:
@@ -378,9 +377,8 @@ def main():
         max_tokens = max(B * CONTEXT, PREFILL_TOKENS) + 64
     else:
         max_tokens = max(B, 64) * CONTEXT + 64
-    model = Model(ModelConfig(compt_type="bfloat16", nr_ctx=CONTEXT, max_tokens=max_tokens, max_batch=max(B, 64)))
+    model = Model(ModelConfig(compt_type="bfloat16", nr_ctx=CONTEXT, max_tokens=max_tokens, max_batch=max(B, 64), gemm=args.gemm))
     model.load_random(cfg, seed=0)
-    ops.set_gemm_backend(args.gemm)
     if args.no_pdl:
         ops.set_pdl(False)
     model.init(top_k=0, top_p=1.0, temp=0.0, repeat_penalty=1.0, repeat_last_n=0, seed=0, end_token=-1)

@@ -1,24 +1,28 @@
-"""Python faces of the CUDA kernels: argument checks, output allocation, the launch.
+"""Single kernels of the library called from Python, for the tests of each kernel alone and for
+the kernel benchmarks (`bench.py --kernels`); the engine does not go through this module.
 
-Every function takes CUDA tensors, launches on torch's current stream and returns
-without synchronising.  A size that a kernel cannot take is refused here with a
-`KernelError` that names it; nothing falls back to another implementation, except that
-the plain matrix product of the bfloat16 mode is the library's (cuBLAS through
-`torch.mm`), as the reference's is (cublasSgemm, src/kern/gpu/kernel_gpu.cu:420-435).
+Every function takes CUDA tensors, allocates the outputs and scratch with torch, launches one
+kernel entry point of `csrc/` on torch's current stream and returns without synchronising.  A size
+that a kernel cannot take is refused with a `KernelError` that names it.  Which kernel the engine
+picks for which sizes is decided in the C++ core (`kernels/ops.h`): `linear`, `linear_gated` and the
+policy functions here ask it, so the choices tested are the ones that run.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
-from .lib import load
+from .. import binding as _b
+from ..binding import KernelError   # noqa: F401
+
+
+def load():
+    return _b.lib()
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 MAX_HEAD_DIM_GENERIC = 256
 MAX_NORM_WIDTH = 200 * 1024 // 4
-
-
-class KernelError(RuntimeError):
-    pass
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
@@ -32,6 +36,61 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+P_, I_, F_, LL_ = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+_KERNEL_SIGNATURES = {
+    "illm_embedding": [P_, P_, I_, P_, I_, I_, I_, P_, P_],
+    "illm_add_rmsnorm": [P_, P_, P_, I_, P_, I_, P_, I_, I_, F_, I_, P_],
+    "illm_residual_add": [P_, P_, I_, LL_, P_],
+    "illm_swiglu": [P_, P_, I_, I_, I_, P_],
+    "illm_rope_kv_write": [P_, P_, P_, P_, P_, I_, P_, P_, I_, I_, I_, I_, I_, I_, I_, I_, I_, P_, P_],
+    "illm_attention_generic": [P_, I_, P_, P_, P_, I_, P_, P_, P_, I_, I_, I_, I_, I_, I_, I_, F_, P_],
+    "illm_attention_decode": [P_, I_, P_, P_, P_, I_, P_, P_, P_, P_, P_, I_, I_, I_, I_, I_, I_, F_, I_, P_],
+    "illm_attention_decode_supported": [I_, I_, I_],
+    "illm_attention_decode_gqa": [P_, I_, P_, P_, P_, I_, P_, P_, P_, P_, P_, I_, I_, I_, I_, I_, I_, F_, I_, P_],
+    "illm_attention_decode_ring": [P_, I_, P_, P_, LL_, P_, I_, P_, P_, P_, P_, P_, I_, I_, I_, I_, I_, I_, F_, I_, P_, P_],
+    "illm_attention_decode_ring_rope": [P_, P_, I_, LL_, P_, I_, I_, I_, P_, P_, LL_, P_, I_, P_, P_, P_, P_, P_, I_, I_, I_, I_, I_, I_,
+                                        F_, I_, P_, P_, P_],
+    "illm_attention_prefill": [P_, I_, P_, P_, P_, I_, P_, P_, P_, I_, I_, I_, I_, I_, I_, I_, F_, P_],
+    "illm_gemm_bf16_tc": [P_, P_, P_, I_, I_, I_, I_, P_, I_, P_, P_, I_],
+    "illm_splitk_reduce": [P_, P_, I_, LL_, I_, P_],
+    "illm_add_rmsnorm_partials": [P_, P_, I_, LL_, P_, I_, P_, I_, P_, I_, I_, F_, I_, P_],
+    "illm_rope_kv_write_partials": [P_, P_, I_, LL_, P_, P_, P_, P_, I_, P_, P_, I_, I_, I_, I_, I_, I_, I_, I_, I_, P_, P_],
+    "illm_gemm_bf16_tc2": [P_, P_, P_, I_, I_, I_, I_, I_, P_, P_],
+    "illm_swiglu_partials": [P_, I_, LL_, P_, I_, I_, P_],
+    "illm_gemm_bf16_tc_gated": [P_, P_, P_, I_, I_, I_, P_, P_],
+    "illm_attention_prefill_tc": [P_, I_, I_, P_, P_, LL_, P_, I_, P_, P_, P_, I_, I_, I_, I_, I_, I_, I_, F_, P_, P_],
+    "illm_gemm_f32_nt": [P_, P_, P_, I_, I_, I_, I_, I_, I_, P_],
+    "illm_argmax": [P_, I_, I_, I_, P_, P_, P_, P_],
+    "illm_sample": [P_, I_, I_, I_, P_, P_, I_, F_, F_, I_, F_, P_, P_, P_, P_],
+    "illm_sample_scratch_elems": [I_, I_, I_, F_],
+    "illm_fill_random": [P_, I_, LL_, ctypes.c_ulonglong, F_, F_, P_],
+    "illm_poison_pages": [P_, P_, LL_, I_, LL_, P_, I_, P_],
+    "illm_selftest_wait_timeout": [P_, P_, LL_, I_, P_],
+}
+_declared = False
+
+
+def _declare():
+    """Argument types of the kernels' own entry points (declared on first use)."""
+    global _declared
+    if _declared:
+        return
+    h = _b.lib()
+    for name, args in _KERNEL_SIGNATURES.items():
+        fn = getattr(h, name)
+        fn.argtypes = args
+        fn.restype = LL_ if name == "illm_sample_scratch_elems" else I_
+    _declared = True
+
+
+_plain_load = load
+
+
+def load():   # noqa: F811
+    _declare()
+    return _plain_load()
+
+
 _replayed = 0
 
 
@@ -39,7 +98,7 @@ def launch_count() -> int:
     """How many kernels of this package have been launched: the library counts every kernel it
     launches (a launch into a stream capture once), replays of captured graphs are added by
     `count_launches`.  Library products (cuBLAS) are not counted."""
-    return int(load().illm_launch_count()) + _replayed
+    return int(_b.lib().illm_launch_count_total()) + _replayed
 
 
 def count_launches(n: int) -> None:
@@ -188,36 +247,31 @@ def swiglu(gu):
     return out
 
 
-# Under "auto" the gate/up product of prompts of 512 tokens and more runs on the package's SM-pair
-# kernel with the activation as its epilogue, so that the packed projection (90 MB per layer at
-# 2,048 tokens of 7B size) never goes to memory: measured on whole prompt steps of a 7B model against
-# the library's product followed by the activation kernel, 6.70 against 7.02 ms at 512 tokens, 12.2
-# against 12.8 at 1,024, 24.1 against 24.5 at 2,048.  Shorter prompts have too few tiles of 256 x 256
-# for the 74 pairs of SMs (86 at 7B size: two rounds for little more than one round's work) and take
-# the library (5.4 against 6.6 ms at 384 tokens, 4.0 against 5.1 at 130).
-GATED_PROMPTS_ON_TC = True
-GATED_PROMPTS_ON_TC_MIN_TOKENS = 512
+def _test_device():
+    """The library's device context for calls outside an engine, on torch's current stream."""
+    dev = ctypes.c_void_p()
+    _b.check(_b.lib().illm_test_device(ctypes.c_void_p(_stream()), ctypes.byref(dev)))
+    return dev
 
 
-def linear_gated(x, w):
+def _take(dev, ptr, shape, dtype, device):
+    out = torch.empty(shape, dtype=dtype, device=device)
+    if out.numel():
+        _b.check(_b.lib().illm_copy_device(dev, out.data_ptr(), ptr, out.numel() * out.element_size()))
+    return out
+
+
+def linear_gated(x, w, backend=None):
     """silu(gate) * up of x [M, K] . w [2I, K]^T, where w's rows 2i, 2i + 1 are the gate and the up
-    row of output i -> [M, I].  Where the package's tcgen05 kernels run the product (see
-    `set_gemm_backend`) the activation is their epilogue and the packed projection never reaches
-    memory; elsewhere it is the product followed by `swiglu`."""
-    M, K = x.shape
-    N = w.shape[0]
-    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M > 0 and K % 8 == 0 and N % 2 == 0
-            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
-        tc = _GEMM_BACKEND == "tc" or (_GEMM_BACKEND == "auto" and M <= GEMM_TC_MAX_TOKENS_AUTO)
-        if tc and M <= 64 and gemm_tc_splits(M, N, K) == 1:
-            out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
-            _check(load().illm_gemm_bf16_tc_gated(_ptr(x), _ptr(w), _ptr(out), M, N, K,
-                                                  _ptr(tc_error_word(x.device)), _stream()), "gemm_bf16_tc_gated")
-            return out
-        if N >= 256 and ((_GEMM_BACKEND == "tc" and M > 128) or (
-                _GEMM_BACKEND == "auto" and GATED_PROMPTS_ON_TC and M >= GATED_PROMPTS_ON_TC_MIN_TOKENS)):
-            return gemm_bf16_tc2(x, w, torch.bfloat16, gated=True)
-    return swiglu(linear(x, w, defer_reduce=True))
+    row of output i -> [M, I], by the kernel the engine picks for these sizes (`ops::linear_gated`)."""
+    _need(x, "x", None, 2)
+    _need(w, "w", x.dtype, 2)
+    dev = _test_device()
+    _b.check(_b.lib().illm_test_device_rewind(dev))
+    out = ctypes.c_void_p()
+    _b.check(_b.lib().illm_op_linear_gated(dev, (backend or _GEMM_BACKEND).encode(), x.data_ptr(), x.shape[0], x.shape[1],
+                                           w.data_ptr(), w.shape[0], act_code(x.dtype), ctypes.byref(out)))
+    return _take(dev, out, (x.shape[0], w.shape[0] // 2), x.dtype, x.device)
 
 
 def rope_kv_write(qkv, cos_sin, rot_dim, token_pos, token_seq, block_table, k_cache, v_cache,
@@ -361,32 +415,10 @@ def attention_decode_ring_supported(dtype, n_heads, n_kv_heads, head_dim, page_s
             and n_heads // n_kv_heads <= 16 and page_size % 64 == 0)
 
 
-def attention_decode_ring_splits(T, n_kv_heads, max_len, head_dim=128) -> int:
-    """Blocks per (token, kv head), by a small model of the kernel's time fitted to measurements
-    (13B size, batch 8, context 4096, 320 pairs: 1 split 129 us, 6 splits 106 us; 160 pairs: 1 split
-    56 us, 2 splits 69 us).  Two blocks fit an SM, so 296 run at once.  Up to that number the kernel
-    streams at the memory rate once about 160 blocks are at work.  Beyond it the blocks run in
-    waves, and a last wave of few blocks still takes 0.43 of a full one (a block alone is bound by
-    what one SM can take in), so a grid a little larger than 296 is the worst and one of many waves
-    is fine again.  Splits cost their partial results and the merge (2.5 us and 0.7 us per split),
-    every wave about 1 us of start-up.  At most one split per 64-key tile and at most 32."""
-    pairs = max(1, T * n_kv_heads)
-    tiles = max(1, -(-int(max_len) // 64))
-    slots = 2 * N_SMS
-    stream_us = pairs * float(max_len) * head_dim * 4 / 6.6e6
-    best, best_us = 1, float("inf")
-    for n in range(1, min(tiles, RING_DECODE_MAX_SPLITS) + 1):
-        blocks = pairs * n
-        waves = blocks / slots
-        if blocks <= slots:
-            stretch = 1.0 / min(1.0, blocks / 160.0)
-        else:
-            full, rest = divmod(blocks, slots)
-            stretch = (full + (max(rest / slots, 0.43) if rest else 0.0)) / waves
-        us = stream_us * stretch + (2.5 + 0.7 * n if n > 1 else 0.0) + 1.0 * -(-blocks // slots)
-        if us < best_us - 1e-9:
-            best, best_us = n, us
-    return best
+def attention_decode_ring_splits(T, n_kv_heads, max_len, head_dim=128, n_sms=None) -> int:
+    """Blocks per (token, kv head) of the ring decode attention: the engine's policy
+    (`ops::attention_decode_ring_splits`), for the SM count of the current device unless given."""
+    return int(_b.lib().illm_policy_ring_splits(int(T), int(n_kv_heads), int(max_len), int(head_dim), int(n_sms or n_sms_of_device())))
 
 
 def attention_decode_ring(qkv, k_cache, v_cache, block_table, token_pos, token_seq, n_heads, n_kv_heads,
@@ -540,16 +572,22 @@ def gemm_f32(x, w):
     return out
 
 
-_tc_err = {}
-N_SMS = 148
+def n_sms_of_device() -> int:
+    """Multiprocessors of the current device (148 without one: what the CPU tests of the policies use)."""
+    if not torch.cuda.is_available():
+        return 148
+    n, tc, st = ctypes.c_int(), ctypes.c_void_p(), ctypes.c_void_p()
+    _b.lib().illm_test_device_info(_test_device(), ctypes.byref(n), ctypes.byref(tc), ctypes.byref(st))
+    return n.value
 
 
-def tc_error_word(device):
-    """The error word of the tensor-core GEMM's bounded waits (one per device)."""
-    key = device.index if device.index is not None else torch.cuda.current_device()
-    if key not in _tc_err:
-        _tc_err[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _tc_err[key]
+def tc_error_word(device=None):
+    """The error word of the tensor-core kernels' bounded waits, of the library's device context for
+    calls outside an engine: an int32 tensor [1] that views it."""
+    from ..engine import device_view
+    n, tc, st = ctypes.c_int(), ctypes.c_void_p(), ctypes.c_void_p()
+    _b.lib().illm_test_device_info(_test_device(), ctypes.byref(n), ctypes.byref(tc), ctypes.byref(st))
+    return device_view(tc.value, (1,), torch.int32, torch.cuda.current_device())
 
 
 class SplitKPartials:
@@ -571,16 +609,10 @@ class SplitKPartials:
         return out
 
 
-def gemm_tc_splits(M, N, K):
-    """How many slices of K a decode-sized product (M <= 64) is cut into, so that about two
-    blocks per SM stream the weights; 1 for larger M."""
-    if M > 64:
-        return 1
-    tiles = -(-N // 128)
-    k_iters = -(-K // 64)
-    splits = max(1, min(2 * N_SMS // tiles, k_iters // 8, 8))     # (more than 8 slices cost their readers more than they win)
-    per = -(-k_iters // splits)
-    return -(-k_iters // per)          # every slice owns at least one 64-wide piece of K
+def gemm_tc_splits(M, N, K, n_sms=None):
+    """How many slices of K a decode-sized product (M <= 64) is cut into: the engine's policy
+    (`ops::gemm_tc_splits`)."""
+    return int(_b.lib().illm_policy_gemm_tc_splits(int(M), int(N), int(K), int(n_sms or n_sms_of_device())))
 
 
 def gemm_bf16_tc(x, w, out_dtype=torch.bfloat16, splits=None, defer_reduce=False):
@@ -614,7 +646,7 @@ def gemm_bf16_tc(x, w, out_dtype=torch.bfloat16, splits=None, defer_reduce=False
 
 def set_pdl(on: bool) -> None:
     """Programmatic dependent launch of the package's kernels (on by default)."""
-    load().illm_set_pdl(1 if on else 0)
+    _b.lib().illm_set_pdl_enabled(1 if on else 0)
 
 
 def gemm_bf16_tc2(x, w, out_dtype=torch.bfloat16, gated=False):
@@ -637,47 +669,37 @@ def gemm_bf16_tc2(x, w, out_dtype=torch.bfloat16, gated=False):
 
 
 _GEMM_BACKEND = "auto"
-GEMM_TC_MAX_TOKENS_AUTO = 16
 
 
 def gemm_backend() -> str:
-    """Which kernels run the bfloat16 products now (`set_gemm_backend`)."""
     return _GEMM_BACKEND
 
 
 def set_gemm_backend(name: str) -> None:
-    """Which kernel runs the bfloat16 matrix products.  "tc": the package's tcgen05 kernels for
-    every product they can take (K a multiple of 8): `gemm_tc.cu` up to 128 tokens, the SM-pair
-    kernel `gemm_tc2.cu` above; "library": cuBLAS through torch.mm; "auto"
-    (default): the tcgen05 kernel for small decode batches (at most 16 tokens), where its swapped,
-    split-K form with weight prefetch across kernel boundaries is faster than the library
-    (74.8 against 89.5 us for the four products of a 7B layer at batch 1, 78.1 against 79.4 at
-    batch 16), and the library for larger ones (at batch 64: 85.5 against 95.7 us)."""
+    """Which kernels `linear` and `linear_gated` of this module ask for when no `backend` is given:
+    "auto" | "tc" | "library" (see `ops::GemmBackend`; an engine has its own setting)."""
     global _GEMM_BACKEND
     if name not in ("tc", "library", "auto"):
         raise ValueError("gemm backend must be 'tc', 'library' or 'auto'")
     _GEMM_BACKEND = name
 
 
-def linear(x, w, out_dtype=None, defer_reduce=False):
-    """x [M, K] . w [N, K]^T.  `defer_reduce=True` allows the result to come back as
-    `SplitKPartials` (only a caller that hands it to `add_rmsnorm` or `rope_kv_write` asks).  float32: the package's own FMA kernel.  bfloat16: the library
-    product with float32 accumulation, rounded to bfloat16 or kept float32 (`out_dtype`)."""
-    if x.dtype == torch.float32:
-        return gemm_f32(x, w)
-    _need(x, "x", torch.bfloat16, 2)
-    _need(w, "w", torch.bfloat16, 2)
-    M, K = x.shape
-    if M > 0 and K % 8 == 0 and (_GEMM_BACKEND == "tc" or (
-            _GEMM_BACKEND == "auto" and M <= GEMM_TC_MAX_TOKENS_AUTO)):
-        if M > 128 and w.shape[0] >= 256:
-            return gemm_bf16_tc2(x, w, out_dtype or torch.bfloat16)      # prompts: pairs of SMs
-        return gemm_bf16_tc(x, w, out_dtype or torch.bfloat16, defer_reduce=defer_reduce)
-    whole = _whole_buckets(x)
-    if whole is not None:
-        x = whole
-    out = torch.mm(x, w.t(), out_dtype=torch.float32) if out_dtype == torch.float32 else torch.mm(x, w.t())
-    return out[:M] if whole is not None else out
+def linear(x, w, out_dtype=None, defer_reduce=False, backend=None):
+    """x [M, K] . w [N, K]^T by the kernel the engine picks for these sizes (`ops::linear`).
+    `defer_reduce=True` allows the result to come back as `SplitKPartials`."""
+    _need(x, "x", None, 2)
+    _need(w, "w", x.dtype, 2)
+    out_dtype = out_dtype or x.dtype
+    dev = _test_device()
+    _b.check(_b.lib().illm_test_device_rewind(dev))
+    out, ws, splits = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_int()
+    M, N = x.shape[0], w.shape[0]
+    _b.check(_b.lib().illm_op_linear(dev, (backend or _GEMM_BACKEND).encode(), x.data_ptr(), M, x.shape[1], w.data_ptr(), N,
+                                     act_code(x.dtype), act_code(out_dtype), 1 if defer_reduce else 0, ctypes.byref(out),
+                                     ctypes.byref(ws), ctypes.byref(splits)))
+    if ws.value:
+        return SplitKPartials(_take(dev, ws, (splits.value, M, N), torch.float32, x.device))
+    return _take(dev, out, (M, N), out_dtype, x.device)
 
 
 def argmax(logits):
@@ -742,12 +764,14 @@ def poison_pages(k, v, pages):
                                     pages.numel(), _stream()), "poison_pages")
 
 
-def selftest_wait_timeout(device, limit_clocks: int = 1 << 20, code: int = 4):
+def selftest_wait_timeout(err=None, limit_clocks: int = 1 << 20, code: int = 4):
     """Runs the bounded mbarrier wait of the tensor-core kernels on a barrier nobody arrives at, with
-    a short limit.  Returns (error word, 1 if the wait reported its time-out, clocks waited); the
-    error word is the device's `tc_error_word`, which is left set for `Engine.check_device_errors`."""
-    err = tc_error_word(device)
-    result = torch.zeros(2, dtype=torch.int64, device=device)
+    a short limit.  `err`: the int32 error word to raise (a tensor [1]; default the word of this
+    module's own device context; `Engine.info()["tc_error_word"]` is an engine's).  Returns (error word,
+    1 if the wait reported its time-out, clocks waited); the word is left set."""
+    if err is None:
+        err = tc_error_word()
+    result = torch.zeros(2, dtype=torch.int64, device=err.device)
     _check(load().illm_selftest_wait_timeout(_ptr(err), _ptr(result), int(limit_clocks), int(code), _stream()),
            "selftest_wait_timeout")
     r = result.tolist()

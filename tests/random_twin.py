@@ -1,6 +1,6 @@
-"""The random numbers of random-weights models in numpy: bit for bit what the device fill kernel
-(`csrc/utility.cu`) and `csrc/random_init.h` compute, so that a model folder written from a seed and
-a model filled on the device from the same seed hold the same tensors.
+"""The random numbers of random-weights models restated in numpy (test infrastructure): the library's
+host generator (model folders) and its device fill kernel (`csrc/utility.cu`) must both give
+these values bit for bit; the definition is that of `csrc/random_init.h`.
 
     key(seed, name) = fnv1a64(name) ^ (seed * G)            G = 0x9E3779B97F4A7C15, 64-bit wrap-around
     base            = fin(key + G)                           fin = the splitmix64 finaliser

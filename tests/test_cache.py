@@ -4,8 +4,7 @@ import random
 import numpy as np
 import pytest
 
-from inferllm_b200.cache import CacheError, CacheFull, IndexPool, PageLedger, SequenceCache
-from inferllm_b200.parts import FixedState, PagedKV
+from inferllm_b200.cache import CacheError, CacheFull, FixedState, IndexPool, PagedKV, PageLedger, SequenceCache
 
 
 def test_pool_alloc_free_reuse():
@@ -74,14 +73,15 @@ def test_window_releases_pages_that_left_the_window():
 def _cache(num_slots=3, num_pages=6, page=4, max_len=16, extra=None):
     reqs = {0: PagedKV(2, 8), 1: PagedKV(2, 8)}
     reqs.update(extra or {})
-    return SequenceCache(reqs, num_slots, num_pages, page, max_len, runtime=None)
+    return SequenceCache(reqs, num_slots, num_pages, page, max_len)
 
 
 def test_groups_by_need():
     c = _cache(extra={2: PagedKV(2, 8, window=5), 3: FixedState((4,)), 4: None})
-    assert len(c.paged) == 2 and len(c.states) == 1
-    assert c.where[0] == ("kv", 0, 0) and c.where[1] == ("kv", 0, 1) and c.where[2] == ("kv", 1, 0)
-    assert c.where[3] == ("state", 0, 0) and 4 not in c.where
+    st = c.stats()
+    assert len(st["paged"]) == 2 and len(st["states"]) == 1
+    assert st["paged"][0]["entries"] == [0, 1] and st["paged"][1]["entries"] == [2] and st["paged"][1]["request"]["window"] == 5
+    assert st["states"][0]["entries"] == [3] and st["states"][0]["request"]["shape"] == [4]
 
 
 def test_step_plan_positions_and_tables():
@@ -146,7 +146,7 @@ def test_freed_slots_and_pages_are_used_again():
         c.free_slot(b)
         c.commit_step(c.plan_step([a], [1]))
         c.free_slot(a)
-        assert c.pages_free() == [4] and c.slots.n_free == 2
+        assert c.pages_free() == [4] and c.slots_free == 2
         c.check()
 
 
@@ -156,7 +156,7 @@ def test_random_walk_keeps_invariants():
     live = {}
     for _ in range(600):
         r = rng.random()
-        if r < 0.25 and c.slots.n_free:
+        if r < 0.25 and c.slots_free:
             live[c.alloc_slot()] = 0
         elif r < 0.45 and live:
             s = rng.choice(list(live))
@@ -180,12 +180,30 @@ def test_random_walk_keeps_invariants():
             for s in chosen:
                 assert c.seq_len[s] == live[s]
                 # every position the next query may see has a page
-                for g in c.paged:
-                    w = g.request.window
+                for gi, g in enumerate(c.stats()["paged"]):
+                    w = g["request"]["window"]
                     lo = max(0, live[s] - w + 1) if w else 0
+                    held = c.pages_of(gi, s)
                     for pos in range(lo, live[s]):
-                        assert pos // 4 in g.ledger.pages[s]
+                        assert pos // 4 in held
         c.check()
     c.reset()
     c.check()
-    assert c.slots.n_free == 5 and c.pages_free() == [12, 12]
+    assert c.slots_free == 5 and c.pages_free() == [12, 12]
+
+
+def test_a_step_that_failed_gives_its_pages_back():
+    """Pages are reserved when a step is planned; if the step does not run, `abandon_step` returns
+    what it had reserved and the sequence stands where it stood."""
+    c = _cache(num_pages=6)
+    s = c.alloc_slot()
+    c.commit_step(c.plan_step([s], [3]))
+    free = c.pages_free()
+    plan = c.plan_step([s], [9])
+    assert c.pages_free()[0] == free[0] - 2
+    c.abandon_step(plan)
+    assert c.pages_free() == free and c.seq_len[s] == 3
+    c.check()
+    c.commit_step(c.plan_step([s], [9]))
+    assert c.seq_len[s] == 12
+    c.check()

@@ -6,9 +6,8 @@ import pytest
 from conftest import TINY
 
 from inferllm_b200 import ConfigError, LlamaConfig, config_from_dict, config_from_folder
-from inferllm_b200.config import ArchConfig, ModelSpec, ScheduleEntry
-from inferllm_b200.registry import (get_architecture, register_architecture,
-                                    registered_architectures, unregister_architecture)
+from inferllm_b200.config import (ArchConfig, ModelSpec, PartSpec, ScheduleEntry, config_class, register_architecture,
+                                  registered_architectures, resolve_architecture, unregister_architecture)
 
 
 def test_every_key_is_read():
@@ -83,8 +82,8 @@ def test_unknown_architecture_lists_registered():
 
 
 def test_reference_model_names_are_aliases():
-    assert get_architecture("llama2") is get_architecture("LlamaForCausalLM")
-    assert get_architecture("llama").config_cls is LlamaConfig
+    assert resolve_architecture("llama2") == resolve_architecture("LlamaForCausalLM") == "LlamaForCausalLM"
+    assert config_class("llama") is LlamaConfig
     assert isinstance(config_from_dict(TINY["A"], model_name="llama2"), LlamaConfig)
 
 
@@ -106,7 +105,9 @@ def test_model_spec_is_data():
     assert m.kind == "attention" and m["n_heads"] == 6 and m["n_kv_heads"] == 2 and m["head_dim"] == 24
     assert m["position"].kind == "rope_half" and m["position"]["theta"] == 500000.0
     assert spec.layers[0].ffn.kind == "gated_mlp" and spec.layers[0].ffn["intermediate_size"] == 384
-    assert spec.layers[2].norm["eps"] == 1e-6 and spec.final_norm["eps"] == 1e-6
+    assert sorted(spec.layers[2].norms) == ["norm1", "norm2"]       # a spec per norm role of the block
+    assert spec.layers[2].norms["norm2"]["eps"] == 1e-6 and spec.final_norm["eps"] == 1e-6
+    assert spec.embedding.kind == "embedding" and spec.head.kind == "lm_head"     # parts of registries like all others
     assert spec.head["tied"] is True and spec.layers[2].prefix == "model.layers.2."
 
 
@@ -127,20 +128,38 @@ def test_schedule_validation():
 
 def test_registering_another_architecture():
     class ToyConfig(ArchConfig):
-        architecture = "ToyForCausalLM"
+        def __init__(self, width=8):
+            self.width = width
 
         @classmethod
         def from_dict(cls, d):
-            return cls()
+            if d.get("width", 8) <= 0:
+                raise ValueError("width must be positive")
+            return cls(d.get("width", 8))
 
-    register_architecture("ToyForCausalLM", ToyConfig, build_model=lambda c, rt: "model")
+        def to_dict(self):
+            return {"architectures": ["ToyForCausalLM"], "width": self.width}
+
+        def model_spec(self):
+            base = config_from_dict(dict(TINY["A"], hidden_size=self.width * 4, head_dim=self.width)).model_spec()
+            base.layers[0].norms["norm2"] = PartSpec("rmsnorm", {"size": self.width * 4, "eps": 0.5})
+            return base
+
+    register_architecture("ToyForCausalLM", ToyConfig, aliases=("toy",))
     try:
-        assert "ToyForCausalLM" in registered_architectures()
-        assert isinstance(config_from_dict({"architectures": ["ToyForCausalLM"]}), ToyConfig)
-        assert get_architecture("ToyForCausalLM").build_model(None, None) == "model"
+        assert "ToyForCausalLM" in registered_architectures() and resolve_architecture("toy") == "ToyForCausalLM"
+        cfg = config_from_dict({"architectures": ["ToyForCausalLM"], "width": 16})
+        assert isinstance(cfg, ToyConfig) and cfg.width == 16
+        # the library sees the Python class's description: its tensors follow the spec the class returned
+        from inferllm_b200.weights import tensor_decls
+        assert tensor_decls(cfg)["model.layers.0.self_attn.q_proj.weight"][0] == (64, 64)
+        with pytest.raises(ConfigError, match="width must be positive"):
+            config_from_dict({"architectures": ["ToyForCausalLM"], "width": 0})
     finally:
         unregister_architecture("ToyForCausalLM")
     assert "ToyForCausalLM" not in registered_architectures()
+    with pytest.raises(ConfigError, match="unknown architecture"):
+        config_from_dict({"architectures": ["ToyForCausalLM"]})
 
 
 def test_command_lines_report_refusals_in_one_line(tmp_path):
@@ -152,7 +171,7 @@ def test_command_lines_report_refusals_in_one_line(tmp_path):
     for prog, args in (("llama", ["-m", str(tmp_path), "--prompt-ids", "1,2"]),
                        ("trace_run", ["--model", str(tmp_path), "--dtype", "float32", "--out", str(tmp_path / "o"),
                                       "--max-tokens", "64"])):
-        r = subprocess.run([sys.executable, os.path.join(root, "bin", prog)] + args, capture_output=True, text=True,
+        r = subprocess.run([os.path.join(root, "bin", prog)] + args, capture_output=True, text=True,
                            stdin=subprocess.DEVNULL, timeout=300)
         assert r.returncode == 1, (prog, r.stderr)
         lines = [ln for ln in r.stderr.splitlines() if ln.strip()]

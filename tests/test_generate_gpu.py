@@ -11,7 +11,7 @@ import pytest
 from conftest import ROOT, TINY, random_prompt
 
 from inferllm_b200 import Model, ModelConfig
-from inferllm_b200.sampling import uniform_for
+from inferllm_b200.sampling import Sampler, SamplingParams, uniform_for
 
 pytestmark = pytest.mark.gpu
 
@@ -51,8 +51,8 @@ def test_warm_up_changes_nothing_and_gives_everything_back(model_folders, plain_
     m.warm_up(prompt_tokens=300, batch_sizes=(1, 2, 5000))
     cache = m.engine.cache
     cache.check()
-    assert cache.slots.n_free == cache.num_slots and cache.pages_free() == [cache.num_pages]
-    assert any(isinstance(v, tuple) for v in m.engine._graphs.values()), "no graph was captured"
+    assert cache.slots_free == cache.num_slots and cache.pages_free() == [cache.num_pages]
+    assert m.engine.info()["graphs_captured"] >= 3, "no graph was captured"
     assert m.generate(prompts, max_new_tokens=6, stop_ids=[]).tokens == want
 
 
@@ -70,7 +70,7 @@ def test_stop_token_ends_early_and_batches_follow_each_other(model_folders, plai
     assert res.batches == [[0, 1], [2, 3], [4]]
     assert res.finish[1] == "stop" and len(res.tokens[1]) <= 4
     m.engine.cache.check()
-    assert m.engine.cache.slots.n_free == 2
+    assert m.engine.cache.slots_free == 2
 
 
 def test_single_conversation_api_of_the_reference(model_folders, plain_models):
@@ -133,22 +133,26 @@ def test_repeat_penalty_changes_greedy_choice(model_folders, plain_models):
 
 @pytest.mark.parametrize("temp", [0.0, 0.9])
 def test_repeat_penalty_with_the_windows_on_the_device(temp, model_folders):
-    """The loop that keeps the host a step behind lets the sampler keep the last tokens on the
-    device; it must choose what the plain loop chooses, which passes the histories from the host
-    at every step (unequal prompts, a window shorter than some prompts, sequences ending early)."""
-    from inferllm_b200.engine import generate, generate_pipelined
-    from inferllm_b200.sampling import Sampler
+    """The library's loop keeps the host a step behind and lets the sampler keep the last tokens on the
+    device; it must choose what a plain loop chooses that passes the histories from the host at every
+    step (unequal prompts, a window shorter than some prompts, sequences ending early).  The plain loop
+    is the tests' own (tests/util.py) over the same engine and the same sampling kernels."""
+    from util import plain_generate
     name = "B"
     prompts = [random_prompt(name, n, 70 + n) for n in (1, 9, 30, 17)]
     m = load(model_folders[name], "float32", nr_ctx=256, max_tokens=1024)
+    params = SamplingParams(temp=temp, top_k=20, top_p=0.9, repeat_penalty=1.4, repeat_last_n=12, seed=5)
     m.init(top_k=20, top_p=0.9, temp=temp, repeat_penalty=1.4, repeat_last_n=12, seed=5, end_token=-1)
-    want = generate(m.engine, prompts, Sampler(m.sampling).choose, 25, [])
-    stop = [want.tokens[2][6]]                       # a token request 2 really samples: it ends early
-    want = generate(m.engine, prompts, Sampler(m.sampling).choose, 25, stop)
-    got = generate_pipelined(m.engine, prompts, Sampler(m.sampling).choose, 25, stop)
-    assert got.tokens == want.tokens and got.finish == want.finish
+    want_tokens, _, _ = plain_generate(m.engine, prompts, Sampler(m.engine, params).choose, 25, [])
+    stop = [want_tokens[2][6]]                       # a token request 2 really samples: it ends early
+    want_tokens, want_finish, _ = plain_generate(m.engine, prompts, Sampler(m.engine, params).choose, 25, stop)
+    got = m.generate(prompts, max_new_tokens=25, stop_ids=stop)
+    assert got.tokens == want_tokens and got.finish == want_finish
     assert "stop" in got.finish and "length" in got.finish
-    assert m.generate(prompts, max_new_tokens=25, stop_ids=stop).tokens == want.tokens
+    # the library's loop driven from Python over the same engine and sampler agrees as well
+    from inferllm_b200.engine import generate
+    again = generate(m.engine, prompts, Sampler(m.engine, params).choose, 25, stop)
+    assert again.tokens == want_tokens and again.finish == want_finish
 
 
 def test_command_line(model_folders, plain_models, tmp_path):
@@ -156,7 +160,7 @@ def test_command_line(model_folders, plain_models, tmp_path):
     cfg, w = plain_models[name]
     prompts = [random_prompt(name, n, 60 + n) for n in (6, 13)]
     want = [plain.greedy_generate(cfg, w, p, 5) for p in prompts]
-    args = [sys.executable, os.path.join(ROOT, "bin", "llama"), "-m", model_folders[name], "-g", "GPU", "-d", "float32",
+    args = [os.path.join(ROOT, "bin", "llama"), "-m", model_folders[name], "-g", "GPU", "-d", "float32",
             "-c", "128", "-n", "5", "--temp", "0", "--top_k", "0", "--top_p", "1", "--repeat_penalty", "1",
             "--no-stop", "-s", "1"]
     for p in prompts:
@@ -166,13 +170,13 @@ def test_command_line(model_folders, plain_models, tmp_path):
     lines = [ln for ln in r.stdout.splitlines() if ln.startswith("[")]
     got = [[int(t) for t in ln.split(": ")[1].split(",")] for ln in lines]
     assert got == want and "decode:" in r.stderr
-    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llama"), "-m", model_folders[name], "-g", "CPU",
+    r = subprocess.run([os.path.join(ROOT, "bin", "llama"), "-m", model_folders[name], "-g", "CPU",
                         "--prompt-ids", "1"], capture_output=True, text=True, timeout=120)
     assert r.returncode == 2 and "CPU" in r.stderr
     # random weights from a config file, no model folder
     cfg_file = tmp_path / "config.json"
     cfg_file.write_text(json.dumps(TINY["B"]))
-    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llama"), "--config", str(cfg_file),
+    r = subprocess.run([os.path.join(ROOT, "bin", "llama"), "--config", str(cfg_file),
                         "--random-weights", "4", "--random-prompts", "3,8", "-n", "4", "-c", "64", "-s", "2"],
                        capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr
@@ -202,7 +206,7 @@ def test_every_end_token_of_the_configuration_stops_by_default(model_folders, pl
     m.init(0, 1.0, 0.0, 1.0, 0, 0, m.end_token)
     res = m.generate([prompt], max_new_tokens=10)
     assert res.tokens == [free[:stop_at + 1]] and res.finish == ["stop"]
-    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llama"), "-m", folder, "-d", "float32", "-c", "128",
+    r = subprocess.run([os.path.join(ROOT, "bin", "llama"), "-m", folder, "-d", "float32", "-c", "128",
                         "-n", "10", "--temp", "0", "--top_k", "0", "--top_p", "1", "--repeat_penalty", "1", "-s", "1",
                         "--prompt-ids", ",".join(map(str, prompt))], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr

@@ -1,9 +1,14 @@
-"""Decisions of the generation loop, with stand-ins for the engine and the sampler (no GPU)."""
+"""Decisions of the library's generation loop, with stand-ins for the engine and the sampler (no
+GPU).  The loop (engine/generate.cpp) keeps the host one step behind the device: sampled tokens feed
+the next step without being looked at, and a sequence that turns out to have sampled a stop token has
+been run one step too far.  Its decisions (which tokens come out, why each request ended, which
+requests ran together) are compared with a plain loop written out below, which looks at every token
+before it takes the next step."""
 import pytest
 
-import torch
+from util import plain_generate
 
-from inferllm_b200.engine import Limits, RequestTooLong, generate, generate_pipelined, plan_batches
+from inferllm_b200.engine import Limits, RequestTooLong, generate, plan_batches
 
 
 class FakeBackend:
@@ -77,10 +82,14 @@ def test_stop_tokens_end_sequences_early_and_are_kept():
     res = generate(be, [[1, 2, 3], [1]], scripted(script), max_new_tokens=5, stop_ids=[9])
     assert res.tokens == [[7, 9], [4, 4, 4, 9]]
     assert res.finish == ["stop", "stop"]
-    # step log: prefill of both, then both, then only request 1 (slot 1) twice
-    assert be.log == [[(0, 3), (1, 1)], [(0, 1), (1, 1)], [(1, 1)], [(1, 1)]]
+    # the prompts, then steps of both requests; request 0 (slot 0) sampled its stop token in the second
+    # step and is seen one step late, so it is stepped once more and then dropped; request 1 likewise
+    assert be.log[0] == [(0, 3), (1, 1)] and be.log[1] == [(0, 1), (1, 1)] and be.log[2] == [(0, 1), (1, 1)]
+    assert all(step == [(1, 1)] for step in be.log[3:]) and len(be.log) == 5
     assert be.len == {} and sorted(be.free) == [0, 1]
-    assert res.decode_steps == 3 and res.decode_tokens == 4 and res.prefill_tokens == 4
+    assert res.prefill_tokens == 4 and res.decode_tokens == 4 and res.decode_steps == 3
+    # what was fed back is what was sampled, in the order of the step's sequences
+    assert be.fed[0] == [7, 4] and be.fed[1] == [9, 4]
 
 
 def test_max_new_tokens_and_no_step_after_the_last_token():
@@ -112,27 +121,27 @@ def test_batches_run_one_after_another_and_reuse_slots():
     assert be.peak_pages <= 4 and be.len == {}
 
 
-def test_history_passed_to_the_chooser_includes_prompt_and_generated():
+def test_the_chooser_gets_the_prompts_once_and_keeps_the_history_itself():
     be = FakeBackend()
     got = []
 
     def choose(logits, requests, steps, histories):
-        got.append([list(h) for h in histories])
+        got.append((list(requests), list(steps), None if histories is None else [list(h) for h in histories]))
         return [9 for _ in requests]
 
-    generate(be, [[1, 2], [3]], choose, max_new_tokens=2)
-    assert got == [[[1, 2], [3]], [[1, 2, 9], [3, 9]]]
+    generate(be, [[1, 2], [3]], choose, max_new_tokens=3)
+    assert got == [([0, 1], [0, 0], [[1, 2], [3]]), ([0, 1], [1, 1], None), ([0, 1], [2, 2], None)]
 
 
 def test_slots_are_returned_when_a_step_raises():
     class Boom(FakeBackend):
-        def step(self, items):
+        def step(self, items, device_ids=None):
             if len(self.log) == 1:
                 raise RuntimeError("boom")
-            return super().step(items)
+            return super().step(items, device_ids)
 
     be = Boom()
-    with pytest.raises(RuntimeError):
+    with pytest.raises(RuntimeError, match="boom"):
         generate(be, [[1], [2]], scripted({0: [5] * 3, 1: [5] * 3}), max_new_tokens=3)
     assert be.len == {} and sorted(be.free) == [0, 1]
 
@@ -140,28 +149,21 @@ def test_slots_are_returned_when_a_step_raises():
 def test_zero_new_tokens():
     be = FakeBackend()
     res = generate(be, [[1]], scripted({0: []}), max_new_tokens=0)
-    assert res.tokens == [[]] and be.log == []
-
-
-def tensor_script(script):
-    def choose(logits, requests, steps, histories):
-        return torch.tensor([script[r][s] for r, s in zip(requests, steps)], dtype=torch.int32)
-    return choose
+    assert res.tokens == [[]] and be.log == [] and res.finish == ["length"]
 
 
 @pytest.mark.parametrize("max_new,stop,max_seq", [(5, [9], 16), (3, [], 16), (10, [9], 6), (1, [9], 16), (4, [7, 4], 16)])
-def test_pipelined_loop_makes_the_same_decisions(max_new, stop, max_seq):
-    """The loop that keeps the host one step behind the device returns what the plain loop
-    returns, feeds the tokens it sampled, and gives every slot back, although sequences that hit
-    a stop token have been run one step too far."""
+def test_the_loop_decides_like_the_plain_loop(max_new, stop, max_seq):
+    """The library's loop returns what the plain loop returns, feeds the tokens it sampled, and gives
+    every slot back, although sequences that hit a stop token have been run one step too far."""
     prompts = [[1, 2, 3], [1], [5, 5], [2, 2, 2, 2], [8]]
     script = {0: [7, 9, 8, 8, 8, 1, 1, 1, 1, 1], 1: [4, 4, 4, 9, 8, 1, 1, 1, 1, 1], 2: [9] * 10, 3: [3] * 10,
               4: [6, 6, 6, 6, 6, 6, 6, 9, 9, 9]}
     a = FakeBackend(max_batch=3, num_pages=12, page_size=4, max_seq_len=max_seq)
     b = FakeBackend(max_batch=3, num_pages=12, page_size=4, max_seq_len=max_seq)
-    want = generate(a, prompts, scripted(script), max_new, stop)
-    got = generate_pipelined(b, prompts, tensor_script(script), max_new, stop)
-    assert got.tokens == want.tokens and got.finish == want.finish and got.batches == want.batches
+    want_tokens, want_finish, want_batches = plain_generate(a, prompts, scripted(script), max_new, stop)
+    got = generate(b, prompts, scripted(script), max_new, stop)
+    assert got.tokens == want_tokens and got.finish == want_finish and got.batches == want_batches
     assert b.len == {} and sorted(b.free) == [0, 1, 2]
     # every token fed back is one that was sampled for that step
     flat = [t for step in b.fed for t in step]
@@ -180,20 +182,30 @@ def test_pipelined_loop_makes_the_same_decisions(max_new, stop, max_seq):
             return snapshot
         return result
     c.read_tokens_async = read_tokens_async
-    again = generate_pipelined(c, prompts, tensor_script(script), max_new, stop)
-    assert again.tokens == want.tokens and again.finish == want.finish and c.len == {}
+    again = generate(c, prompts, scripted(script), max_new, stop)
+    assert again.tokens == want_tokens and again.finish == want_finish and c.len == {}
     assert c.reads >= 1
 
 
-@pytest.mark.parametrize("loop,script_of", [(generate, scripted), (generate_pipelined, tensor_script)])
-def test_a_batch_is_stepped_longest_prompt_first(loop, script_of):
-    """Both loops put a batch's sequences into every step longest first (the attention kernels hand
-    out their blocks in that order) and keep the results by request."""
+def test_a_batch_is_stepped_longest_prompt_first():
+    """The loop puts a batch's sequences into every step longest first (the attention kernels hand
+    out their blocks in that order) and keeps the results by request."""
     prompts = [[1], [1, 2, 3, 4, 5], [1, 2], [1, 2, 3]]
     script = {r: [10 + r] * 3 for r in range(4)}
     be = FakeBackend(max_batch=4, num_pages=16, page_size=4, max_seq_len=16)
-    res = loop(be, prompts, script_of(script), 3, [])
+    res = generate(be, prompts, scripted(script), 3, [])
     assert res.tokens == [[10 + r] * 3 for r in range(4)]
     assert [n for _, n in be.log[0]] == [5, 3, 2, 1]               # the prompts, longest first
     first = [slot for slot, _ in be.log[0]]
     assert all([slot for slot, _ in step] == first for step in be.log[1:3])   # and so in the steps after
+
+
+def test_timing_uses_the_callers_clock():
+    t = [0.0]
+
+    def clock():
+        t[0] += 1.0
+        return t[0]
+
+    res = generate(FakeBackend(), [[1, 2]], scripted({0: [5, 6, 7]}), max_new_tokens=3, clock=clock)
+    assert res.decode_steps == 2 and res.prefill_s > 0 and res.decode_s > 0 and len(res.step_s) == 2

@@ -34,6 +34,19 @@ def err_word():
     return torch.zeros(1, dtype=torch.int32, device="cuda")
 
 
+def library_rope_table(d, rot, theta, positions):
+    """The cos/sin table that the library's own rotate-half position encoding builds for these
+    constants: float32 [positions, rot / 2, 2] (a copy)."""
+    from inferllm_b200.config import PartSpec
+    from inferllm_b200.engine import device_view
+    from inferllm_b200.parts import PartSandbox
+    sandbox = PartSandbox({}, "bfloat16")
+    part = sandbox.build("position", PartSpec("rope_half", dict(head_dim=d, rot_dim=rot, theta=theta, max_positions=positions)))
+    info = part.describe()
+    assert info["rot_dim"] == rot and info["positions"] == positions and info["takes_partials"]
+    return device_view(info["rotation_table"], (positions, rot // 2, 2), torch.float32).clone()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("V,H", [(50, 24), (1000, 4096), (333, 1001)])
 def test_embedding(dtype, V, H):
@@ -268,17 +281,13 @@ def test_unreduced_split_k_slices_feed_norm_and_rope():
     wq = (torch.randn((nh + 2 * nkv) * d, 4096, generator=g) * 0.05).bfloat16()
     part = ops.gemm_bf16_tc(dev(x), dev(wq), defer_reduce=True, splits=4)
     qkv_full = part.materialize(torch.float32)
-    from inferllm_b200.config import PartSpec
-    from inferllm_b200.parts import Runtime, build_part
-    rope = build_part("position", PartSpec("rope_half", dict(head_dim=d, theta=1e4, max_positions=64)),
-                      Runtime(torch.device("cuda"), torch.bfloat16))
-    rope.prepare()
+    rope_table = library_rope_table(d, d, 1e4, 64)
     kc = torch.zeros(4, nkv, page, d, dtype=torch.bfloat16, device="cuda")
     vc = torch.zeros_like(kc)
     table = torch.tensor([[2, 0]], dtype=torch.int32).cuda()
     pos = torch.tensor([3, 4, 5, 16, 17], dtype=torch.int32).cuda()
     seq = torch.zeros(M, dtype=torch.int32).cuda()
-    out = ops.rope_kv_write(part, rope.table, d, pos, seq, table, kc, vc, nh, nkv, d, page, True, err_word())
+    out = ops.rope_kv_write(part, rope_table, d, pos, seq, table, kc, vc, nh, nkv, d, page, True, err_word())
     src = f64(qkv_full).reshape(M, nh + 2 * nkv, d)
     want = plain.rope_rotate_half(src[:, :nh + nkv], pos.cpu().numpy(), 1e4)
     assert maxrel(f64(out).reshape(M, nh + 2 * nkv, d)[:, :nh], want[:, :nh]) <= 2 ** -8
@@ -289,12 +298,10 @@ def test_unreduced_split_k_slices_feed_norm_and_rope():
     # a rotation over the first 32 of the 64 channels only: the other channels of Q and K are the sums
     # of the slices, unrotated
     rot = 32
-    rope32 = build_part("position", PartSpec("rope_half", dict(head_dim=d, rot_dim=rot, theta=1e4, max_positions=64)),
-                        Runtime(torch.device("cuda"), torch.bfloat16))
-    rope32.prepare()
+    rope32_table = library_rope_table(d, rot, 1e4, 64)
     kc.zero_()
     vc.zero_()
-    out = ops.rope_kv_write(part, rope32.table, rot, pos, seq, table, kc, vc, nh, nkv, d, page, True, err_word())
+    out = ops.rope_kv_write(part, rope32_table, rot, pos, seq, table, kc, vc, nh, nkv, d, page, True, err_word())
     want = plain.rope_rotate_half(src[:, :nh + nkv], pos.cpu().numpy(), 1e4, rot_dim=rot)
     assert maxrel(f64(out).reshape(M, nh + 2 * nkv, d)[:, :nh], want[:, :nh]) <= 2 ** -8
     for i, p_ in enumerate(pos.tolist()):
@@ -609,12 +616,7 @@ def test_attention_decode_ring_with_the_position_encoding_inside(nh, nkv, d, pag
     scale = 1.0 / math.sqrt(d)
     table = None
     if rot:
-        from inferllm_b200.config import PartSpec
-        from inferllm_b200.parts import Runtime, build_part
-        rope = build_part("position", PartSpec("rope_half", dict(head_dim=d, rot_dim=rot, theta=1e4, max_positions=2048)),
-                          Runtime(torch.device("cuda"), torch.bfloat16))
-        rope.prepare()
-        table = rope.table
+        table = library_rope_table(d, rot, 1e4, 2048)
     # the two kernels: rotation and cache write (from the slices, as the engine would), then attention
     kc1, vc1 = dev(pc.kc), dev(pc.vc)
     src = ops.SplitKPartials(part.ws.clone()) if slices else qkv_bf16.clone()
@@ -709,8 +711,6 @@ def test_attention_window_edge(dtype):
 @pytest.mark.parametrize("nh,nkv,d,rot,page,theta", [(4, 4, 16, 16, 8, 1e4), (6, 2, 24, 24, 16, 5e5),
                                                      (3, 1, 128, 64, 64, 1e6), (2, 2, 64, 0, 32, 1e4)])
 def test_rope_and_cache_write(dtype, nh, nkv, d, rot, page, theta):
-    from inferllm_b200.config import PartSpec
-    from inferllm_b200.parts import Runtime, build_part
     lens = [70, 5]
     starts = [64, 0]      # sequence 0 appends positions 64..69, sequence 1 is a new prompt
     pc = Paged(lens, nkv, d, page, DT[dtype], seed=3)
@@ -722,11 +722,7 @@ def test_rope_and_cache_write(dtype, nh, nkv, d, rot, page, theta):
     pos = torch.tensor([r[1] for r in rows], dtype=torch.int32)
     table = None
     if rot:
-        rt = Runtime(torch.device("cuda"), DT[dtype])
-        part = build_part("position", PartSpec("rope_half", dict(head_dim=d, rot_dim=rot, theta=theta,
-                                                                 max_positions=128)), rt)
-        part.prepare()
-        table = part.table
+        table = library_rope_table(d, rot, theta, 128)
     kc, vc, x = dev(pc.kc), dev(pc.vc), dev(qkv)
     err = err_word()
     ops.rope_kv_write(x, table, rot, dev(pos), dev(seq), dev(pc.table), kc, vc, nh, nkv, d, page, True, err)
@@ -760,12 +756,8 @@ def test_rope_and_cache_write(dtype, nh, nkv, d, rot, page, theta):
 def test_rope_angles_at_far_positions_match_float64():
     """theta^(-2j/d) * p for p in the thousands: a table computed in float32 arithmetic would be
     off by 1e-4 and more; the kernel's table is float64 rounded once."""
-    from inferllm_b200.config import PartSpec
-    from inferllm_b200.parts import Runtime, build_part
     d = 128
-    part = build_part("position", PartSpec("rope_half", dict(head_dim=d, theta=1e4, max_positions=8192)),
-                      Runtime(torch.device("cuda"), torch.float32))
-    part.prepare()
+    far_table = library_rope_table(d, d, 1e4, 8192)
     pos = np.array([8191, 4097, 1])
     x = np.zeros((3, 1, d))
     x[:, :, :d // 2] = 1.0
@@ -775,7 +767,7 @@ def test_rope_angles_at_far_positions_match_float64():
     kc = torch.zeros(130, 1, 64, d, device="cuda")
     tab = torch.arange(129, dtype=torch.int32).reshape(1, 129).cuda()
     t = dev(qkv)
-    ops.rope_kv_write(t, part.table, d, dev(torch.tensor(pos, dtype=torch.int32)),
+    ops.rope_kv_write(t, far_table, d, dev(torch.tensor(pos, dtype=torch.int32)),
                       dev(torch.zeros(3, dtype=torch.int32)), tab, kc, kc.clone(), 1, 1, d, 64, True, err_word())
     assert np.abs(f64(t)[:, :d] - ref[:, 0]).max() <= 2e-7
 
@@ -877,7 +869,7 @@ def test_sample_large_vocabulary_and_greedy_limit():
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("n,std,mean", [(1, 0.02, 0.0), (1000, 0.02, 1.0), (300007, 0.5, 0.0)])
 def test_fill_random_is_the_numpy_twin_bit_for_bit(dtype, n, std, mean):
-    from inferllm_b200.weights.random_init import random_key, random_values, to_bfloat16_bits
+    from random_twin import random_key, random_values, to_bfloat16_bits
     key = random_key(7, "model.layers.1.mlp.up_proj.weight")
     out = ops.fill_random(torch.empty(n, dtype=DT[dtype], device="cuda"), key, std, mean).cpu()
     want = random_values(7, "model.layers.1.mlp.up_proj.weight", n, std, mean)
@@ -908,11 +900,10 @@ def test_a_wait_that_runs_out_sets_the_error_word_and_the_kernel_returns():
     short limit, on a barrier at which nothing ever arrives.  The kernel comes back by itself, the
     wait tells its caller that it gave up, the device's error word names the kernel family, and
     the device goes on working."""
-    device = torch.device("cuda")
-    word = ops.tc_error_word(device)
+    word = ops.tc_error_word()
     word.zero_()
     for code in (4, 5, 7):
-        got, gave_up, clocks = ops.selftest_wait_timeout(device, limit_clocks=1 << 18, code=code)
+        got, gave_up, clocks = ops.selftest_wait_timeout(word, limit_clocks=1 << 18, code=code)
         assert (got, gave_up) == (code, 1)
         assert (1 << 18) <= clocks < (1 << 24)
         word.zero_()

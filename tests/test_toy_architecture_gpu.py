@@ -1,8 +1,10 @@
 """A toy architecture defined here, registered, built and stepped without a change to the
-package's files (GPU): layers with different mixers, a mixer with fixed-size state of its own,
-another position encoding, a feed-forward with routing, a layer that runs twice and a layer that
-reads another layer's cache.  It is no model of
-anyone's; it shows that the seams hold."""
+library's files (GPU): layers with different mixers, a mixer with fixed-size state of its own,
+another position encoding, a feed-forward with routing, two norms of one block that differ, a layer
+that runs twice and a layer that reads another layer's cache.  The parts are written in Python over
+the library's interface for parts in other languages (the library calls them on every step); the
+architecture is a Python class whose spec the library builds its generic decoder from.  It is no model
+of anyone's; it shows that the seams hold."""
 from dataclasses import dataclass
 
 import numpy as np
@@ -12,14 +14,14 @@ import torch
 from util import rel_err
 
 from inferllm_b200 import Engine, EngineOptions, StepItem, write_random_model
-from inferllm_b200.config import ArchConfig, LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+from inferllm_b200.config import (ArchConfig, LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture,
+                                  unregister_architecture)
 from inferllm_b200.kernels import ops
-from inferllm_b200.parts import (FeedForward, FixedState, Mixer, PositionEncoding, TensorDecl,
-                                 register_feed_forward, register_mixer, register_position)
-from inferllm_b200.registry import register_architecture, unregister_architecture
+from inferllm_b200.parts import (FeedForward, FixedState, Mixer, PositionEncoding, TensorDecl, register_feed_forward,
+                                 register_mixer, register_position, unregister_part)
 
 pytestmark = pytest.mark.gpu
-H, NH, NKV, D, I, V, EPS, THETA = 48, 3, 1, 16, 80, 97, 1e-5, 1e4
+H, NH, NKV, D, I, V, EPS, EPS2, THETA = 48, 3, 1, 16, 80, 97, 1e-5, 3e-3, 1e4
 
 
 @register_mixer("toy_running_mean")
@@ -39,12 +41,12 @@ class RunningMean(Mixer):
         self.w = tensors["mix.weight"].float()
 
     def cache_request(self):
-        return FixedState((self.h + 1,), torch.float32)
+        return FixedState((self.h + 1,), "float32")
 
     def forward(self, h, ctx, cache, writes):
         out = torch.empty_like(h)
         off = 0
-        slots = ctx.slots.tolist()
+        slots = ctx.host_slots
         for b, q in enumerate(ctx.q_lens):
             st = cache.state[slots[b]]
             x = h[off:off + q].float()
@@ -117,17 +119,17 @@ class Top1Experts(FeedForward):
 @dataclass
 class ToyConfig(ArchConfig):
     n_positions: int = 128
-    architecture = "ToyMixForCausalLM"
 
     @classmethod
     def from_dict(cls, d):
         return cls(n_positions=d.get("n_positions", 128))
 
     def to_dict(self):
-        return {"architectures": [self.architecture], "n_positions": self.n_positions}
+        return {"architectures": ["ToyMixForCausalLM"], "n_positions": self.n_positions}
 
     def model_spec(self):
         norm = PartSpec("rmsnorm", {"size": H, "eps": EPS})
+        norm_b = PartSpec("rmsnorm", {"size": H, "eps": EPS2})      # the second norm of a block is another one
         att = PartSpec("attention", {"hidden_size": H, "n_heads": NH, "n_kv_heads": NKV, "head_dim": D,
                                      "window": None, "position": PartSpec("rope_half", {
                                          "head_dim": D, "theta": THETA, "max_positions": self.n_positions})})
@@ -137,7 +139,7 @@ class ToyConfig(ArchConfig):
                                            "window": None, "position": PartSpec("toy_pairs", {"theta": THETA})})
         routed = PartSpec("toy_top1_experts", {})
         names = {"mixer": "mixer.", "ffn": "ffn.", "norm1": "ln1.", "norm2": "ln2."}
-        layers = [LayerSpec("prenorm", m, f, norm, f"blocks.{i}.", dict(names))
+        layers = [LayerSpec("prenorm", m, f, {"norm1": norm, "norm2": norm_b}, f"blocks.{i}.", dict(names))
                   for i, (m, f) in enumerate([(att, ffn), (mean, ffn), (att, ffn), (att_pairs, routed)])]
         # layer 0, layer 1 (state), layer 0 again (a second cache entry), layer 2 reading entry 0,
         # layer 3 with the other position encoding and the routed feed-forward
@@ -172,7 +174,7 @@ def plain_layer3(w, x, pos):
     sc = plain.scale_and_mask(plain.attention_scores(q, k, NH, NKV), D ** -0.5)
     o = plain.weighted_values(plain.softmax_rows(sc), v, NH, NKV)
     x = x + plain.linear(o, w[p + "mixer.o_proj.weight"])
-    h = plain.rms_norm(x, w[p + "ln2.weight"], EPS)
+    h = plain.rms_norm(x, w[p + "ln2.weight"], EPS2)
     logits = plain.linear(h, w[p + "ffn.router.weight"])
     top = np.sort(logits, -1)
     margin = top[:, -1] - top[:, -2]
@@ -202,7 +204,7 @@ def plain_toy(w, ids):
             if entry == 0 and writes:
                 kv0 = kv
         x = x + a
-        h = plain.rms_norm(x, w[p + "ln2.weight"], EPS)
+        h = plain.rms_norm(x, w[p + "ln2.weight"], EPS2)
         x = x + plain.swiglu_ffn(h, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"],
                                  w[p + "ffn.down_proj.weight"])
     x, margin = plain_layer3(w, x, pos)
@@ -216,6 +218,8 @@ def toy_folder(tmp_path_factory):
     write_random_model(ToyConfig(), d, seed=3, dtype=torch.float32)
     yield d
     unregister_architecture("ToyMixForCausalLM")
+    for family, kind in (("mixer", "toy_running_mean"), ("position", "toy_pairs"), ("feed_forward", "toy_top1_experts")):
+        unregister_part(family, kind)
 
 
 @pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 4e-2)])
@@ -224,8 +228,10 @@ def test_toy_architecture_steps_like_its_plain_twin(toy_folder, dtype, tol):
     if dtype == "bfloat16":   # the engine rounds the stored float32 matrices; give the twin the same
         w = {k: (torch.tensor(v).bfloat16().double().numpy() if "ln" not in k else v) for k, v in w.items()}
     eng = Engine.from_folder(toy_folder, EngineOptions(dtype=dtype, max_tokens=512, page_size=16, max_batch=3))
-    assert len(eng.cache.paged) == 1 and len(eng.cache.paged[0].entries) == 3   # entries 0, 2 and 3
-    assert len(eng.cache.states) == 1 and eng.cache.states[0].state.shape == (1, 3, H + 1)
+    st = eng.cache.stats()
+    assert len(st["paged"]) == 1 and st["paged"][0]["entries"] == [0, 2, 3]
+    assert len(st["states"]) == 1 and tuple(eng.state_tensor(0).shape) == (1, 3, H + 1)
+    assert eng.info()["graph_safe"] is False        # the toy mixer reads the step's host fields
     rng = np.random.default_rng(0)
     reqs = [rng.integers(0, V, n).tolist() for n in (70, 9, 33, 50)]
     both = [plain_toy(w, r) for r in reqs]

@@ -18,8 +18,7 @@ TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
 
 def replay(folder, dtype, steps, out_dir, max_tokens):
     """Feed the steps one at a time, waiting for `done <step>` after each."""
-    exe = [os.environ["ILLM_TRACE_RUN_EXE"]] if os.environ.get("ILLM_TRACE_RUN_EXE") else [sys.executable, TRACE_RUN]
-    proc = subprocess.Popen([*exe, "--model", folder, "--dtype", dtype, "--out", out_dir,
+    proc = subprocess.Popen([TRACE_RUN, "--model", folder, "--dtype", dtype, "--out", out_dir,
                              "--max-tokens", str(max_tokens)], stdin=subprocess.PIPE, stdout=subprocess.PIPE,
                             text=True)
     try:

@@ -71,8 +71,8 @@ def _plain_rows(qkv, kc, vc, table, lens, nh, nkv, d, page, window, scale, which
 
 
 def test_static_scratch_entry_point_matches_the_regular_one():
+    from inferllm_b200.binding import lib as load
     from inferllm_b200.kernels import ops
-    from inferllm_b200.kernels.lib import load
 
     P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
     fn = load().illm_attention_decode_static

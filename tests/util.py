@@ -1,4 +1,6 @@
-"""Helpers of the GPU tests: tolerances and engine construction."""
+"""Helpers of the tests: tolerances, engine construction, and a plain generation loop (the oracle of
+the library's loop: it looks at every token before it takes the next step and hands the chooser the
+whole history every time)."""
 import numpy as np
 
 # Bounds on max |difference| relative to max |reference| of the compared block.  float32: a few
@@ -42,28 +44,40 @@ def make_engine(folder, dtype, max_tokens=1024, page_size=64, max_batch=None, ma
         max_seq_len=max_seq_len, poison_freed_pages=poison))
 
 
-class PartHarness:
-    """The minimum an engine gives a part under test: a runtime, a cache for the part's request
-    and step contexts made the way the engine makes them."""
+def _ints(toks):
+    return [int(t) for t in (toks.tolist() if hasattr(toks, "tolist") else toks)]
 
-    def __init__(self, requests, dtype, num_slots=4, num_pages=16, page_size=16, max_seq_len=256):
-        import torch
 
-        from inferllm_b200.cache import SequenceCache
-        from inferllm_b200.parts import Runtime
-        self.rt = Runtime(torch.device("cuda"), {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype],
-                          page_size)
-        self.cache = SequenceCache(requests, num_slots, num_pages, page_size, max_seq_len, self.rt)
-        self.err = torch.zeros(1, dtype=torch.int32, device="cuda")
-        self._stages = [(None, None, None)] * 4
-        self._stage_next = 0
-
-    def _upload(self, parts, offs, total, into=None):
-        from inferllm_b200.engine import Engine
-        return Engine._upload(self, parts, offs, total, into)
-
-    def context(self, slots, q_lens, ids=None, want=()):
-        from inferllm_b200.engine import StepContext
-        plan = self.cache.plan_step(slots, q_lens)
-        ctx = StepContext(self, plan, ids if ids is not None else [0] * sum(q_lens), list(want))
-        return ctx, plan
+def plain_generate(backend, prompts, choose, max_new_tokens, stop_ids=()):
+    """The same decisions without any overlap: step, choose, look, then step again."""
+    from inferllm_b200.engine import StepItem, plan_batches
+    limits, stop = backend.limits(), set(stop_ids)
+    tokens, finish = [[] for _ in prompts], [""] * len(prompts)
+    batches = plan_batches([len(p) for p in prompts], max_new_tokens, limits)
+    for batch in batches:
+        slots = {r: backend.new_sequence() for r in batch}
+        hist = {r: list(prompts[r]) for r in batch}
+        live = sorted(batch, key=lambda r: -len(prompts[r]))
+        toks = _ints(choose(backend.step([StepItem(slots[r], list(prompts[r]), [len(prompts[r]) - 1]) for r in live]), live,
+                            [0] * len(live), [hist[r] for r in live]))
+        while True:
+            nxt = []
+            for r, tok in zip(live, toks):
+                tokens[r].append(tok)
+                hist[r].append(tok)
+                if tok in stop:
+                    finish[r] = "stop"
+                elif len(tokens[r]) >= max_new_tokens:
+                    finish[r] = "length"
+                elif len(hist[r]) > limits.max_seq_len:
+                    finish[r] = "context"
+                else:
+                    nxt.append(r)
+                    continue
+                backend.end_sequence(slots.pop(r))
+            live = nxt
+            if not live:
+                break
+            toks = _ints(choose(backend.step([StepItem(slots[r], [hist[r][-1]], [0]) for r in live]), live,
+                                [len(tokens[r]) for r in live], [hist[r] for r in live]))
+    return tokens, finish, batches
