@@ -87,7 +87,7 @@ _SIGNATURES = {
     "illm_engine_create": [P, S, PP], "illm_engine_from_folder": [S, S, S, PP], "illm_engine_free": [P],
     "illm_engine_load_folder": [P, S], "illm_engine_load_random": [P, ULL], "illm_engine_new_sequence": [P, PI],
     "illm_engine_end_sequence": [P, I], "illm_engine_sequence_length": [P, I, PLL], "illm_engine_limits": [P, PLL],
-    "illm_engine_step": [P, I, PI, PI, PI, PI, PI, P, P, PP], "illm_engine_warm_up": [P, LL, PI, I],
+    "illm_engine_step": [P, I, PI, PI, PI, PI, PI, P, P, PP, P], "illm_engine_order": [P, P, I], "illm_engine_warm_up": [P, LL, PI, I],
     "illm_engine_check_device_errors": [P], "illm_engine_cache": [P], "illm_engine_info": [P, PP], "illm_engine_set_gemm": [P, S],
     "illm_launch_count_total": [], "illm_set_pdl_enabled": [I], "illm_uniform_for": [LL, LL, LL],
     "illm_sampling_params_validate": [S], "illm_sampler_create": [P, S, PP], "illm_sampler_free": [P],

@@ -71,18 +71,39 @@ ILLM_API int illm_engine_limits(void* e, long long out[4]) {
         out[3] = l.max_seq_len;
     });
 }
+// A caller's stream as the binding passes it: 0 means none; the legacy default stream is given as
+// cudaStreamLegacy (1).
+static cudaStream_t caller_stream(void* s) { return (cudaStream_t)s; }
+
 // Runs one step.  The logits [sum of n_want, vocab] are copied to `logits_out` (device, float32) if it
-// is not null; *logits_dev gets the engine's own copy (valid until its next step).
+// is not null; *logits_dev gets the engine's own copy (valid until its next step).  `caller`: the
+// stream on which the caller made device_ids and will read logits_out (nullptr: none): the engine's
+// stream waits for it before the step, and it waits for the engine's stream after the step; the host
+// waits for neither.
 ILLM_API int illm_engine_step(void* e, int n_items, const int* slots, const int* n_tokens, const int* tokens, const int* n_want,
-                              const int* want, const int* device_ids, float* logits_out, const float** logits_dev) {
+                              const int* want, const int* device_ids, float* logits_out, const float** logits_dev, void* caller) {
     return guard([&] {
         Engine* eng = (Engine*)e;
+        eng->device().make_current();
+        if (caller) eng->device().wait_for(caller_stream(caller));
         LogitsRef lg = eng->step(items_from(n_items, slots, n_tokens, tokens, n_want, want), device_ids);
         if (logits_dev) *logits_dev = lg.p;
         if (logits_out && lg.rows > 0)
             check_cuda(cudaMemcpyAsync(logits_out, lg.p, (size_t)lg.rows * lg.vocab * sizeof(float), cudaMemcpyDeviceToDevice,
                                        eng->device().stream()),
                        "copying the logits");
+        if (caller) eng->device().signal_to(caller_stream(caller));
+    });
+}
+// Orders the engine's stream against a caller's: direction 0: the engine waits for the caller;
+// 1: the caller waits for the engine.
+ILLM_API int illm_engine_order(void* e, void* caller, int direction) {
+    return guard([&] {
+        Engine* eng = (Engine*)e;
+        eng->device().make_current();
+        if (!caller) return;
+        if (direction == 0) eng->device().wait_for(caller_stream(caller));
+        else eng->device().signal_to(caller_stream(caller));
     });
 }
 ILLM_API int illm_engine_warm_up(void* e, long long prompt_tokens, const int* batch_sizes, int n) {
@@ -153,7 +174,7 @@ ILLM_API void illm_sampler_free(void* s) { delete (Sampler*)s; }
 // device, valid for the sampler's next three calls.
 ILLM_API int illm_sampler_choose(void* s, const float* logits, int B, long long V, const int* requests, const int* steps,
                                  const int* hist_lens, const int* hist, const int** tokens) {
-    return guard([&] {
+    return guard([&] {     // (the caller orders the streams with illm_engine_order around this call)
         std::vector<std::vector<int>> hs;
         if (hist_lens) {
             size_t off = 0;

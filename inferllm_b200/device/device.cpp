@@ -51,6 +51,7 @@ Device::Device(int ordinal, cudaStream_t stream) : ordinal_(ordinal) {
 Device::~Device() {
     cudaSetDevice(ordinal_);
     cudaStreamSynchronize(stream_);
+    if (order_event_) cudaEventDestroy(order_event_);
     for (SmallStage& st : small_) {
         if (st.host) cudaFreeHost(st.host);
         if (st.done) cudaEventDestroy(st.done);
@@ -69,6 +70,19 @@ void Device::set_stream(cudaStream_t s) {
     own_stream_ = false;
     stream_ = s;
     cublasSetStream((cublasHandle_t)cublas_, stream_);
+}
+
+void Device::wait_for(cudaStream_t other) {
+    if (other == stream_) return;
+    if (!order_event_) check_cuda(cudaEventCreateWithFlags(&order_event_, cudaEventDisableTiming), "cudaEventCreate");
+    check_cuda(cudaEventRecord(order_event_, other), "cudaEventRecord");
+    check_cuda(cudaStreamWaitEvent(stream_, order_event_, 0), "cudaStreamWaitEvent");
+}
+void Device::signal_to(cudaStream_t other) {
+    if (other == stream_) return;
+    if (!order_event_) check_cuda(cudaEventCreateWithFlags(&order_event_, cudaEventDisableTiming), "cudaEventCreate");
+    check_cuda(cudaEventRecord(order_event_, stream_), "cudaEventRecord");
+    check_cuda(cudaStreamWaitEvent(other, order_event_, 0), "cudaStreamWaitEvent");
 }
 
 void Device::make_current() const { check_cuda(cudaSetDevice(ordinal_), "cudaSetDevice"); }

@@ -41,6 +41,11 @@ public:
     int n_sms() const { return n_sms_; }
     cudaStream_t stream() const { return stream_; }
     void set_stream(cudaStream_t s);
+    // Ordering against another stream of the same device (a caller that exchanges device memory with
+    // the engine works on its own stream): this stream waits for what `other` holds now / `other` waits
+    // for what this stream holds now.  Neither blocks the host.
+    void wait_for(cudaStream_t other);
+    void signal_to(cudaStream_t other);
     void make_current() const;
     void synchronize() const;
     size_t mem_free() const;
@@ -85,6 +90,7 @@ private:
     int *tc_err_ = nullptr, *step_err_ = nullptr;
     void* cublas_ = nullptr;
     void* cublas_ws_ = nullptr;
+    cudaEvent_t order_event_ = nullptr;
     struct SmallStage { char* host = nullptr; size_t cap = 0; cudaEvent_t done = nullptr; bool used = false; };
     SmallStage small_[8];
     int small_next_ = 0;

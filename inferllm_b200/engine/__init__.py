@@ -1,7 +1,9 @@
 """The engine, the programming entry point and the generation loop as Python sees them: thin faces
 over the C++ core (`engine/engine.h`, `engine/model_api.h`, `engine/generate.h`).  Token ids go in as
-Python lists; logits come back as float32 torch tensors on the device the engine runs on, computed
-on torch's current stream (the engine is given that stream when it is made)."""
+Python lists; logits come back as float32 torch tensors on the device the engine runs on.  The engine
+works on a CUDA stream of its own; every call that exchanges device memory with torch orders that
+stream against torch's current stream (the one waits for the other, the host for neither), so the
+tensors can be used like the results of any torch operation."""
 from __future__ import annotations
 
 import ctypes
@@ -53,12 +55,19 @@ class StepItem:
     want: Sequence[int] = field(default_factory=list)  # places among `tokens` whose logits are asked for
 
 
-def _current_stream(device_id: int) -> int:
+def _need_cuda(device_id: int) -> None:
     import torch
     if not torch.cuda.is_available():
         raise EngineError("inferllm_b200 needs a CUDA device: there is no CPU path")
     torch.cuda.set_device(device_id)
-    return int(torch.cuda.current_stream(device_id).cuda_stream)
+
+
+def caller_stream(device_id: Optional[int] = None) -> ctypes.c_void_p:
+    """torch's current stream as the library takes a caller's stream: the legacy default stream
+    (handle 0) is named by CUDA's cudaStreamLegacy (1), since 0 means "none" there."""
+    import torch
+    s = int(torch.cuda.current_stream(device_id).cuda_stream)
+    return ctypes.c_void_p(s if s else 1)
 
 
 def _flatten(items):
@@ -79,8 +88,8 @@ class Engine:
         self._cache = None
         if _ptr is None:
             out = ctypes.c_void_p()
-            _b.check(_b.lib().illm_engine_create(config.handle(), options.to_json(_current_stream(options.device_id)).encode(),
-                                                 ctypes.byref(out)))
+            _need_cuda(options.device_id)
+            _b.check(_b.lib().illm_engine_create(config.handle(), options.to_json(0).encode(), ctypes.byref(out)))
             _ptr = out
         self._ptr = _ptr
         self.config = config
@@ -142,7 +151,7 @@ class Engine:
         out = torch.empty((len(want), self.vocab_size), dtype=torch.float32, device=f"cuda:{self.device_id}")
         _b.check(_b.lib().illm_engine_step(self._ptr, len(slots), _b.ints(slots), _b.ints(n_tok), _b.ints(toks), _b.ints(n_want),
                                            _b.ints(want), device_ids.data_ptr() if device_ids is not None else None,
-                                           out.data_ptr() if len(want) else None, None))
+                                           out.data_ptr() if len(want) else None, None, caller_stream(self.device_id)))
         return out
 
     def warm_up(self, prompt_tokens: int = 0, batch_sizes: Sequence[int] = ()) -> None:
@@ -189,10 +198,14 @@ class Engine:
         dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}[g["request"]["dtype"]]
         return device_view(g["state"], (len(g["entries"]), st["num_slots"], *g["request"]["shape"]), dtype, self.device_id)
 
+    def order(self, direction: int) -> None:
+        """0: the engine's stream waits for what torch's current stream holds now; 1: the other way round."""
+        _b.check(_b.lib().illm_engine_order(self._ptr, caller_stream(self.device_id), direction))
+
     def _copy(self, dst: int, src: int, nbytes: int) -> None:
-        import torch
+        """Copy device memory on torch's current stream."""
         dev = ctypes.c_void_p()
-        _b.check(_b.lib().illm_test_device(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), ctypes.byref(dev)))
+        _b.check(_b.lib().illm_test_device(caller_stream(self.device_id), ctypes.byref(dev)))
         _b.check(_b.lib().illm_copy_device(dev, ctypes.c_void_p(dst), ctypes.c_void_p(src), nbytes))
 
 
@@ -379,7 +392,7 @@ class Model:
         d["max_tokens"] = config.max_tokens or 0
         d["max_batch"] = config.max_batch or 0
         if config.device_type.lower() in ("gpu", "cuda"):
-            d["stream"] = _current_stream(config.device_id)
+            _need_cuda(config.device_id)
         out = ctypes.c_void_p()
         _b.check(_b.lib().illm_model_create(json.dumps(d).encode(), _b.enc(model_name), ctypes.byref(out)))
         self._ptr = out

@@ -250,7 +250,7 @@ def swiglu(gu):
 def _test_device():
     """The library's device context for calls outside an engine, on torch's current stream."""
     dev = ctypes.c_void_p()
-    _b.check(_b.lib().illm_test_device(ctypes.c_void_p(_stream()), ctypes.byref(dev)))
+    _b.check(_b.lib().illm_test_device(ctypes.c_void_p(_stream() or 1), ctypes.byref(dev)))    # 1: cudaStreamLegacy (0 would mean "none")
     return dev
 
 

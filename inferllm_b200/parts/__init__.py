@@ -49,6 +49,13 @@ class TensorDecl:
     init: str = "matrix"
 
 
+def _torch_stream(handle):
+    """The step's stream as a torch stream (cudaStreamLegacy, 1, is torch's default stream)."""
+    import torch
+    h = int(handle or 0)
+    return torch.cuda.default_stream() if h in (0, 1) else torch.cuda.ExternalStream(h)
+
+
 def _torch_dtype(code: int):
     import torch
     return {0: torch.float32, 1: torch.bfloat16, 5: torch.int32}[code]
@@ -217,7 +224,7 @@ def _register(family: str, kind: str, cls):
     def mixer_forward(_u, instance, step, cache, h, out, T, H, writes):
         part, s = instances[instance], step.contents
         dev = device_of(s)
-        with torch.cuda.stream(torch.cuda.ExternalStream(s.stream or 0)):
+        with torch.cuda.stream(_torch_stream(s.stream)):
             ctx = StepView(s, dev)
             x = device_view(h, (T, H), ctx.dtype, dev)
             y = part.forward(x, ctx, _cache_view(cache.contents, s.B, dev), bool(writes))
@@ -226,7 +233,7 @@ def _register(family: str, kind: str, cls):
     def ffn_forward(_u, instance, step, h, out, T, H):
         part, s = instances[instance], step.contents
         dev = device_of(s)
-        with torch.cuda.stream(torch.cuda.ExternalStream(s.stream or 0)):
+        with torch.cuda.stream(_torch_stream(s.stream)):
             ctx = StepView(s, dev)
             y = part.forward(device_view(h, (T, H), ctx.dtype, dev), ctx)
             device_view(out, (T, H), ctx.dtype, dev).copy_(y)
@@ -234,7 +241,7 @@ def _register(family: str, kind: str, cls):
     def encode_and_store(_u, instance, step, cache, qkv, T, width, nh, nkv, d):
         part, s = instances[instance], step.contents
         dev = device_of(s)
-        with torch.cuda.stream(torch.cuda.ExternalStream(s.stream or 0)):
+        with torch.cuda.stream(_torch_stream(s.stream)):
             ctx = StepView(s, dev)
             x = device_view(qkv, (T, width), ctx.dtype, dev)
             y = part.encode_and_store(x, (nh, nkv, d), ctx, KVCacheView(cache.contents, s.B, dev))
@@ -361,7 +368,7 @@ class PartSandbox:
         reqs = {str(k): (None if v is None else v.to_json()) for k, v in requests.items()}
         out = ctypes.c_void_p()
         _b.check(_b.lib().illm_sandbox_create(json.dumps(reqs).encode(), dtype.encode(), num_slots, num_pages, page_size, max_seq_len,
-                                              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), ctypes.byref(out)))
+                                              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream or 1), ctypes.byref(out)))
         self._ptr = out
         self.cache = SequenceCache.wrap(_b.lib().illm_sandbox_cache(out), self)
         self._dev = ctypes.c_void_p(_b.lib().illm_sandbox_device(out))

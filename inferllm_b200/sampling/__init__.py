@@ -56,8 +56,10 @@ class Sampler:
             lens = _b.ints(len(h) for h in histories)
             hist = _b.ints(t for h in histories for t in h)
         out = ctypes.c_void_p()
+        self._engine.order(0)           # the sampler works on the engine's stream: it waits for the logits
         _b.check(_b.lib().illm_sampler_choose(self._ptr, logits.data_ptr(), B, V, _b.ints(requests), _b.ints(steps), lens, hist,
                                               ctypes.byref(out)))
+        self._engine.order(1)
         toks = torch.empty(B, dtype=torch.int32, device=logits.device)
         self._engine._copy(toks.data_ptr(), out.value, 4 * B)
         return toks
