@@ -86,6 +86,7 @@ class Engine:
         self.options = options
         self._owner = _owner
         self._cache = None
+        self._children = []       # weak references to samplers made on this engine: they go before it does
         if _ptr is None:
             out = ctypes.c_void_p()
             _need_cuda(options.device_id)
@@ -97,10 +98,22 @@ class Engine:
         self.vocab_size = info["vocab_size"]
         self.device_id = info["device"]
 
+    def _adopt(self, child) -> None:
+        import weakref
+        self._children.append(weakref.ref(child))
+
+    def _release_children(self) -> None:
+        for ref in getattr(self, "_children", []):
+            child = ref()
+            if child is not None:
+                child._free()
+        self._children = []
+
     def __del__(self):
+        self._release_children()
         if getattr(self, "_owner", None) is None and getattr(self, "_ptr", None) and _b._lib is not None:
             _b._lib.illm_engine_free(self._ptr)
-            self._ptr = None
+        self._ptr = None
 
     # ---- construction
 
@@ -272,8 +285,11 @@ def generate(backend, prompts: Sequence[Sequence[int]], choose: Callable, max_ne
     PI, PLL = ctypes.POINTER(I), ctypes.POINTER(LL)
     objects, reads, error = {}, {}, []
 
+    counter = [0]
+
     def keep(obj) -> int:
-        h = len(objects) + 1
+        counter[0] += 1
+        h = counter[0]
         objects[h] = obj
         if len(objects) > 64:
             objects.pop(min(objects))
@@ -398,18 +414,24 @@ class Model:
         self._ptr = out
         self._engine = None
 
+    def _drop_engine(self) -> None:
+        if self._engine is not None:
+            self._engine._release_children()
+            self._engine._ptr = None
+            self._engine = None
+
     def __del__(self):
         if getattr(self, "_ptr", None) and _b._lib is not None:
-            self._engine = None
+            self._drop_engine()
             _b._lib.illm_model_free(self._ptr)
             self._ptr = None
 
     def load(self, model_path: str) -> None:
-        self._engine = None
+        self._drop_engine()
         _b.check(_b.lib().illm_model_load(self._ptr, model_path.encode()))
 
     def load_random(self, config: ArchConfig, seed: int = 0) -> None:
-        self._engine = None
+        self._drop_engine()
         _b.check(_b.lib().illm_model_load_random(self._ptr, config.handle(), int(seed)))
 
     @property

@@ -299,11 +299,15 @@ class _Proxy:
         out = ctypes.c_void_p()
         _b.check(_b.lib().illm_sandbox_build(sandbox._ptr, family.encode(), json.dumps(spec.to_json()).encode(), ctypes.byref(out)))
         self._ptr = out
-        self._kept = None
+        sandbox._adopt(self)
+
+    def _free(self) -> None:
+        if getattr(self, "_ptr", None) and _b._lib is not None and getattr(self.sandbox, "_ptr", None):
+            _b._lib.illm_part_free(self._ptr)       # (its tensors live on the sandbox's device)
+        self._ptr = None
 
     def __del__(self):
-        if getattr(self, "_ptr", None) and _b._lib is not None:
-            _b._lib.illm_part_free(self._ptr)
+        self._free()
 
     def describe(self) -> dict:
         return _b.call_json(_b.lib().illm_part_describe, self._ptr)
@@ -339,10 +343,15 @@ class ResidualStream:
         out = ctypes.c_void_p()
         _b.check(_b.lib().illm_stream_create(sandbox._ptr, x.data_ptr(), x.shape[0], x.shape[1], ctypes.byref(out)))
         self._ptr = out
+        sandbox._adopt(self)
+
+    def _free(self) -> None:
+        if getattr(self, "_ptr", None) and _b._lib is not None and getattr(self.sandbox, "_ptr", None):
+            _b._lib.illm_stream_free(self._ptr)
+        self._ptr = None
 
     def __del__(self):
-        if getattr(self, "_ptr", None) and _b._lib is not None:
-            _b._lib.illm_stream_free(self._ptr)
+        self._free()
 
     def add(self, delta) -> None:
         import torch
@@ -373,11 +382,21 @@ class PartSandbox:
         self.cache = SequenceCache.wrap(_b.lib().illm_sandbox_cache(out), self)
         self._dev = ctypes.c_void_p(_b.lib().illm_sandbox_device(out))
         self.B = 0
+        self._children = []      # weak references to parts, streams and blocks: they go before the device does
+
+    def _adopt(self, child) -> None:
+        import weakref
+        self._children.append(weakref.ref(child))
 
     def __del__(self):
+        for ref in getattr(self, "_children", []):
+            child = ref()
+            if child is not None:
+                child._free()
         if getattr(self, "_ptr", None) and _b._lib is not None:
             self.cache = None
             _b._lib.illm_sandbox_free(self._ptr)
+        self._ptr = None
 
     def build(self, family: str, spec: PartSpec) -> _Proxy:
         return _Proxy(self, family, spec)
@@ -451,10 +470,15 @@ def block_norm_roles(kind: str):
 class _Block:
     def __init__(self, sandbox, ptr, parts):
         self.sandbox, self._ptr, self._parts = sandbox, ptr, parts
+        sandbox._adopt(self)
+
+    def _free(self) -> None:
+        if getattr(self, "_ptr", None) and _b._lib is not None and getattr(self.sandbox, "_ptr", None):
+            _b._lib.illm_block_free(self._ptr)
+        self._ptr = None
 
     def __del__(self):
-        if getattr(self, "_ptr", None) and _b._lib is not None:
-            _b._lib.illm_block_free(self._ptr)
+        self._free()
 
     def forward(self, stream: ResidualStream, entry=0, writes=True):
         _b.check(_b.lib().illm_sandbox_block_forward(self.sandbox._ptr, self._ptr, stream._ptr, entry, 1 if writes else 0))

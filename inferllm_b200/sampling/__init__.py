@@ -43,10 +43,18 @@ class Sampler:
         out = ctypes.c_void_p()
         _b.check(_b.lib().illm_sampler_create(engine._ptr, json.dumps(asdict(params)).encode(), ctypes.byref(out)))
         self._ptr = out
+        engine._adopt(self)
+
+    def _free(self) -> None:
+        # (the sampler's buffers live on the engine's device: once the engine is gone they are gone too,
+        # and the library's object must not be touched any more)
+        engine = getattr(self, "_engine", None)
+        if getattr(self, "_ptr", None) and _b._lib is not None and engine is not None and engine._ptr:
+            _b._lib.illm_sampler_free(self._ptr)
+        self._ptr = None
 
     def __del__(self):
-        if getattr(self, "_ptr", None) and _b._lib is not None:
-            _b._lib.illm_sampler_free(self._ptr)
+        self._free()
 
     def choose(self, logits, requests: Sequence[int], steps: Sequence[int], histories: Optional[Sequence[List[int]]] = None):
         import torch
@@ -55,6 +63,8 @@ class Sampler:
         if histories is not None:
             lens = _b.ints(len(h) for h in histories)
             hist = _b.ints(t for h in histories for t in h)
+        if not self._ptr:
+            raise _b.EngineError("the sampler's engine is gone")
         out = ctypes.c_void_p()
         self._engine.order(0)           # the sampler works on the engine's stream: it waits for the logits
         _b.check(_b.lib().illm_sampler_choose(self._ptr, logits.data_ptr(), B, V, _b.ints(requests), _b.ints(steps), lens, hist,
