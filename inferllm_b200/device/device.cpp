@@ -59,7 +59,8 @@ Device::~Device() {
     if (cublas_) cublasDestroy((cublasHandle_t)cublas_);
     if (cublas_ws_) cudaFree(cublas_ws_);
     if (tc_err_) cudaFree(tc_err_);
-    for (Block& b : blocks_) cudaFree(b.base);
+    for (Lane& lane : lanes_)
+        for (Block& b : lane.blocks) cudaFree(b.base);
     if (own_stream_) cudaStreamDestroy(stream_);
 }
 
@@ -122,38 +123,58 @@ void Device::free_persistent(void* p) {
 void* Device::alloc(size_t bytes) {
     bytes = (bytes + 255) & ~(size_t)255;
     if (bytes == 0) bytes = 256;
-    while (cur_ < blocks_.size()) {
-        Block& b = blocks_[cur_];
+    Lane& lane = lanes_[lane_];
+    while (lane.cur < lane.blocks.size()) {
+        Block& b = lane.blocks[lane.cur];
         if (b.used + bytes <= b.size) {
             void* p = b.base + b.used;
             b.used += bytes;
             return p;
         }
-        cur_++;
-        if (cur_ < blocks_.size()) blocks_[cur_].used = 0;
+        lane.cur++;
+        if (lane.cur < lane.blocks.size()) lane.blocks[lane.cur].used = 0;
     }
-    // a new block: at least 64 MiB, at least as large as all blocks so far (so their number stays small)
+    // a new block: at least 64 MiB, and at least half of what the lane holds (so the blocks stay few)
     size_t held = 0;
-    for (Block& b : blocks_) held += b.size;
-    const size_t size = std::max<size_t>({bytes, held, (size_t)64 << 20});
+    for (Block& b : lane.blocks) held += b.size;
+    const size_t size = std::max<size_t>({bytes, held / 2, (size_t)64 << 20});
     Block nb;
     nb.base = (char*)alloc_persistent(size, "the step's working memory");
     nb.size = size;
     nb.used = bytes;
-    blocks_.push_back(nb);
-    cur_ = blocks_.size() - 1;
+    lane.blocks.push_back(nb);
+    lane.cur = lane.blocks.size() - 1;
     arena_generation_++;
     return nb.base;
 }
 
+void Device::set_lane(int lane, bool rewind) {
+    lane_ = lane;
+    if (rewind) {
+        lanes_[lane].cur = 0;
+        if (!lanes_[lane].blocks.empty()) lanes_[lane].blocks[0].used = 0;
+    }
+}
+
 void Device::arena_rewind() {
-    cur_ = 0;
-    if (!blocks_.empty()) blocks_[0].used = 0;
+    for (int l = 0; l < kLanes; l++) set_lane(l, true);
+    lane_ = 0;
+}
+
+void Device::arena_release() {
+    synchronize();
+    for (Lane& lane : lanes_) {
+        for (Block& b : lane.blocks) cudaFree(b.base);
+        lane.blocks.clear();
+        lane.cur = 0;
+    }
+    lane_ = 0;
 }
 
 size_t Device::arena_bytes() const {
     size_t held = 0;
-    for (const Block& b : blocks_) held += b.size;
+    for (const Lane& lane : lanes_)
+        for (const Block& b : lane.blocks) held += b.size;
     return held;
 }
 

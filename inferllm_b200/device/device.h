@@ -4,12 +4,16 @@
 // Memory comes in two kinds.  Persistent blocks (weights, cache pages, tables, inputs and outputs of
 // captured graphs) are taken from the driver one by one and live until they are freed.  Everything a
 // step computes on its way (activations, partial results, scratch of kernels) comes from the step
-// arena: a list of large blocks from which allocations are cut off in order and which is rewound,
-// not freed, when the next step begins.  The same sequence of allocations therefore gets the same
-// addresses every time, which is what lets a step be captured in a CUDA graph and replayed, and no
-// step pays the driver for memory once the arena has seen its size.  The arena only grows: a block
-// is never given back or moved while the device lives, so addresses inside captured graphs stay
-// valid.  The reference's counterpart is its Device with a free-list pool per size
+// arena: lists of large blocks from which allocations are cut off in order and which are rewound,
+// not freed.  The same sequence of allocations therefore gets the same addresses every time, which
+// is what lets a step be captured in a CUDA graph and replayed, and no step pays the driver for
+// memory once the arena has seen its size.  The arena has three lanes: lane 0 holds what lives for
+// the whole step (its index arrays, the residual stream, the logits); lanes 1 and 2 take turns
+// layer by layer, and a lane is rewound when its turn comes again, so a step holds the activations
+// of two layers, not of all (what a layer hands to the next one, its last product's output, is read
+// by the next layer's first norm, before that layer's own lane comes round again).  The arena only
+// grows while steps run: a block is never given back or moved, so addresses inside captured graphs
+// stay valid.  The reference's counterpart is its Device with a free-list pool per size
 // (src/core/device.cpp: allocate / free_device) and a workspace that is re-sized when the token
 // count changes (src/core/graph.cpp:169-180).
 #pragma once
@@ -55,9 +59,12 @@ public:
     void free_persistent(void* p);
 
     // the step arena
-    void* alloc(size_t bytes);                 // 256-byte aligned; valid until the arena is rewound
+    static constexpr int kLanes = 3;
+    void* alloc(size_t bytes);                 // from the current lane; 256-byte aligned; valid until that lane is rewound
     template <typename T> T* alloc_n(size_t n) { return (T*)alloc(n * sizeof(T)); }
-    void arena_rewind();                       // a new step begins
+    void arena_rewind();                       // a new step begins: all lanes rewound, lane 0 current
+    void set_lane(int lane, bool rewind);      // allocate from this lane from now on (rewound first if asked)
+    void arena_release();                      // give all blocks back to the driver (only while no captured graph uses them)
     size_t arena_bytes() const;                // what the arena holds from the driver
     unsigned long long arena_generation() const { return arena_generation_; }   // grows whenever a block was added
 
@@ -81,11 +88,12 @@ public:
 
 private:
     struct Block { char* base; size_t size, used; };
+    struct Lane { std::vector<Block> blocks; size_t cur = 0; };
     int ordinal_, n_sms_ = 148;
     cudaStream_t stream_ = nullptr;
     bool own_stream_ = false;
-    std::vector<Block> blocks_;
-    size_t cur_ = 0;
+    Lane lanes_[kLanes];
+    int lane_ = 0;
     unsigned long long arena_generation_ = 0;
     int *tc_err_ = nullptr, *step_err_ = nullptr;
     void* cublas_ = nullptr;

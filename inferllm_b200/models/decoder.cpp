@@ -72,8 +72,13 @@ std::map<int, CacheRequest> DecoderModel::cache_requests() const {
 }
 
 Mat DecoderModel::forward(const StepContext& ctx, const SequenceCache& cache, const std::vector<const int*>& tables_dev) {
+    Device& dev = *rt->dev;
     ResidualStream stream = embedding_->forward(ctx);
+    int turn = 0;
     for (const ScheduleEntry& e : spec.schedule) {
+        // the layers' activations take turns in two lanes of the step arena: what a layer leaves for the
+        // next one (its last output, pending in the stream) is read before this lane's turn comes again
+        dev.set_lane(1 + (turn++ & 1), true);
         CacheView view;
         switch (cache.kind_of(e.cache)) {
             case SequenceCache::KV:
@@ -89,6 +94,7 @@ Mat DecoderModel::forward(const StepContext& ctx, const SequenceCache& cache, co
         }
         layers_[(size_t)e.layer].block->forward(stream, ctx, view, e.writes);
     }
+    dev.set_lane(0, false);
     if (ctx.K == 0) {
         Mat none;
         none.cols = spec.vocab_size;

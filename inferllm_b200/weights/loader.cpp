@@ -206,8 +206,7 @@ void load_model_weights(DecoderModel& model, const std::string& folder) {
     model.load_tensors([&](const std::string& prefix) {
         return std::unique_ptr<TensorSource>(new FileSource(model.rt, &files.records, &inits, prefix, &up));
     });
-    model.rt->dev->synchronize();
-    model.rt->dev->arena_rewind();
+    model.rt->dev->arena_release();        // what the conversions needed goes back to the driver
 }
 
 void init_random_weights(DecoderModel& model, unsigned long long seed) {
@@ -217,8 +216,7 @@ void init_random_weights(DecoderModel& model, unsigned long long seed) {
     model.load_tensors([&](const std::string& prefix) {
         return std::unique_ptr<TensorSource>(new RandomSource(model.rt, &decls, prefix, seed));
     });
-    model.rt->dev->synchronize();
-    model.rt->dev->arena_rewind();
+    model.rt->dev->arena_release();
 }
 
 float random_value(unsigned long long seed, const std::string& name, long long i, const std::string& init) {
