@@ -85,9 +85,12 @@ ILLM_API int illm_engine_step(void* e, int n_items, const int* slots, const int*
     return guard([&] {
         Engine* eng = (Engine*)e;
         eng->device().make_current();
-        if (caller) eng->device().wait_for(caller_stream(caller));
+        // the step itself waits for the caller only if it reads the caller's memory; the copy into the
+        // caller's buffer waits in any case (the buffer may still be in use on the caller's stream)
+        if (caller && device_ids) eng->device().wait_for(caller_stream(caller));
         LogitsRef lg = eng->step(items_from(n_items, slots, n_tokens, tokens, n_want, want), device_ids);
         if (logits_dev) *logits_dev = lg.p;
+        if (caller && !device_ids && logits_out && lg.rows > 0) eng->device().wait_for(caller_stream(caller));
         if (logits_out && lg.rows > 0)
             check_cuda(cudaMemcpyAsync(logits_out, lg.p, (size_t)lg.rows * lg.vocab * sizeof(float), cudaMemcpyDeviceToDevice,
                                        eng->device().stream()),
