@@ -289,7 +289,9 @@ def run_scenario(args, cfg, cfgd, model_name, L, fig, pk, pk_src):
     model = Model(ModelConfig(compt_type="bfloat16", nr_ctx=ctx, max_tokens=max_tokens, max_batch=B, gemm=args.gemm))
     model.load_random(cfg, seed=0)
     model.init(top_k=0, top_p=1.0, temp=0.0, repeat_penalty=1.0, repeat_last_n=0, seed=0, end_token=-1)
-    model.generate([p[:64] for p in prompts], max_new_tokens=4, stop_ids=[])       # compile, capture
+    # warm-up with the same prompts: the step's working memory has grown to this step's size, the
+    # library has chosen its kernels for these shapes, the decode graph of this batch is captured
+    model.generate(prompts, max_new_tokens=4, stop_ids=[])
     with ClockSampler() as cs:
         res = model.generate(prompts, max_new_tokens=new, stop_ids=[])
     steps = res.step_s[max(3, args.warmup):]

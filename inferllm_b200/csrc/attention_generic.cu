@@ -9,7 +9,7 @@
 // product Q K^T (src/kern/gpu/kernel_gpu.cu:576-591), scale + causal mask (:504-536), a
 // three-pass row softmax (:78-125) and the batched product with V (:593-609); formulas
 // src/kern/naive/naive.cpp:606-632, :531-553, :209-240, :664-691, grouped heads :576-604.
-// Here one block owns one (token, head): its four warps walk the keys lo..p in blocks of 32
+// Here one block owns one (token, head): its sixteen warps walk the keys lo..p in blocks of 32
 // (a key per lane for the scores, a channel per lane for the values) with a running maximum
 // and sum, and are merged in a fixed order.  The split of the keys depends only on the
 // token's own position and window, so its result does not depend on the step it is part of.
@@ -18,7 +18,7 @@
 
 #include "common.cuh"
 
-#define AG_WARPS 4
+#define AG_WARPS 16
 #define AG_MAX_D 256
 
 template <typename TA>
@@ -60,6 +60,7 @@ attention_generic_kernel(const TA* __restrict__ q, int q_stride, const TA* __res
             off = (((long long)page * nkv + hk) * page_size + (key % page_size)) * d;
             const TA* kr = kc + off;
             float dot = 0.f;
+#pragma unroll 4
             for (int c = 0; c < d; c += 8) {
                 float f[8];
                 load8(kr + c, f);
@@ -75,6 +76,7 @@ attention_generic_kernel(const TA* __restrict__ q, int q_stride, const TA* __res
 #pragma unroll
         for (int i = 0; i < AG_MAX_D / 32; i++) acc[i] *= corr;
         const int nk = (p - kb + 1 < 32) ? p - kb + 1 : 32;
+#pragma unroll 4
         for (int j = 0; j < nk; j++) {
             const float pj = __shfl_sync(0xffffffffu, pe, j);
             const long long oj = __shfl_sync(0xffffffffu, off, j);

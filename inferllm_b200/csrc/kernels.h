@@ -36,7 +36,7 @@ int illm_set_pdl(int on);
 long long illm_launch_count();
 
 // gemm_f32.cu
-int illm_gemm_f32_nt(const float* A, const float* W, float* C, int M, int N, int K, int lda, int ldw, int ldc, void* stream);
+int illm_gemm_f32_nt(const float* A, const float* W, float* C, int M, int N, int K, int lda, int ldw, int ldc, int* err, void* stream);
 
 // gemm_tc.cu
 int illm_gemm_bf16_tc_tune(int stages);

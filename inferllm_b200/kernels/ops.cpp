@@ -225,7 +225,7 @@ Mat gemm_f32(Device& dev, const Mat& x, const Mat& w) {
     for (long long m0 = 0; m0 < M; m0 += 65535LL * 64) {
         const long long m1 = std::min(M, m0 + 65535LL * 64);
         check_kernel(illm_gemm_f32_nt((const float*)row_ptr(x, m0), (const float*)w.p, (float*)row_ptr(out, m0), (int)(m1 - m0), (int)N, (int)K,
-                                      (int)K, (int)K, (int)N, dev.stream()),
+                                      (int)K, (int)K, (int)N, dev.tc_error_word(), dev.stream()),
                      "gemm_f32");
     }
     return out;

@@ -59,7 +59,7 @@ _KERNEL_SIGNATURES = {
     "illm_swiglu_partials": [P_, I_, LL_, P_, I_, I_, P_],
     "illm_gemm_bf16_tc_gated": [P_, P_, P_, I_, I_, I_, P_, P_],
     "illm_attention_prefill_tc": [P_, I_, I_, P_, P_, LL_, P_, I_, P_, P_, P_, I_, I_, I_, I_, I_, I_, I_, F_, P_, P_],
-    "illm_gemm_f32_nt": [P_, P_, P_, I_, I_, I_, I_, I_, I_, P_],
+    "illm_gemm_f32_nt": [P_, P_, P_, I_, I_, I_, I_, I_, I_, P_, P_],
     "illm_argmax": [P_, I_, I_, I_, P_, P_, P_, P_],
     "illm_sample": [P_, I_, I_, I_, P_, P_, I_, F_, F_, I_, F_, P_, P_, P_, P_],
     "illm_sample_scratch_elems": [I_, I_, I_, F_],
@@ -252,6 +252,20 @@ def _test_device():
     dev = ctypes.c_void_p()
     _b.check(_b.lib().illm_test_device(ctypes.c_void_p(_stream() or 1), ctypes.byref(dev)))    # 1: cudaStreamLegacy (0 would mean "none")
     return dev
+
+
+_info_dev = None
+
+
+def _info_device():
+    """One device context whose error word and figures serve every call of this module outside an
+    engine, whatever torch's current stream is (a context of its own per stream would be created,
+    with an allocation, inside a stream capture)."""
+    global _info_dev
+    if _info_dev is None:
+        _info_dev = ctypes.c_void_p()
+        _b.check(_b.lib().illm_test_device(ctypes.c_void_p(1), ctypes.byref(_info_dev)))
+    return _info_dev
 
 
 def _take(dev, ptr, shape, dtype, device):
@@ -568,7 +582,7 @@ def gemm_f32(x, w):
     for m0 in range(0, M, 65535 * 64):
         m1 = min(M, m0 + 65535 * 64)
         _check(load().illm_gemm_f32_nt(_ptr(x[m0:m1]), _ptr(w), _ptr(out[m0:m1]), m1 - m0, N, K, K, K,
-                                       N, _stream()), "gemm_f32")
+                                       N, _ptr(tc_error_word(x.device)), _stream()), "gemm_f32")
     return out
 
 
@@ -577,7 +591,7 @@ def n_sms_of_device() -> int:
     if not torch.cuda.is_available():
         return 148
     n, tc, st = ctypes.c_int(), ctypes.c_void_p(), ctypes.c_void_p()
-    _b.lib().illm_test_device_info(_test_device(), ctypes.byref(n), ctypes.byref(tc), ctypes.byref(st))
+    _b.lib().illm_test_device_info(_info_device(), ctypes.byref(n), ctypes.byref(tc), ctypes.byref(st))
     return n.value
 
 
@@ -586,7 +600,7 @@ def tc_error_word(device=None):
     calls outside an engine: an int32 tensor [1] that views it."""
     from ..engine import device_view
     n, tc, st = ctypes.c_int(), ctypes.c_void_p(), ctypes.c_void_p()
-    _b.lib().illm_test_device_info(_test_device(), ctypes.byref(n), ctypes.byref(tc), ctypes.byref(st))
+    _b.lib().illm_test_device_info(_info_device(), ctypes.byref(n), ctypes.byref(tc), ctypes.byref(st))
     return device_view(tc.value, (1,), torch.int32, torch.cuda.current_device())
 
 
@@ -776,3 +790,4 @@ def selftest_wait_timeout(err=None, limit_clocks: int = 1 << 20, code: int = 4):
            "selftest_wait_timeout")
     r = result.tolist()
     return int(err.item()), int(r[0]), int(r[1])
+
