@@ -139,7 +139,7 @@ SCENARIOS = {"8b": "16:64:2048:256", "13b": "32:128:1024:to4096", "7b": "8:512:5
 REF_LIKE_LAYERS = 4            # layers of the model that the reference arm runs (baseline/reference_arm.py)
 
 
-def run_kernels(pk, pk_src):
+def run_kernels(pk, pk_src, only=None):
     """The hot kernels one by one at several sizes (beside the contract): each is replayed from a
     CUDA graph of several launches on different buffers (so that nothing is served from L2 by the
     launch before), timed with events, and printed as one JSON line with its algorithmic bytes or
@@ -153,12 +153,18 @@ def run_kernels(pk, pk_src):
     dev = torch.device("cuda")
     torch.manual_seed(0)
 
+    side = torch.cuda.Stream()
+
     def graph_us(fns, reps=10):
-        for f in fns:
-            f()
+        # warm-up and capture on one stream: the library keeps a context (working memory, error word)
+        # per stream for calls outside an engine, which has to exist before the capture begins
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for f in fns:
+                f()
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        with torch.cuda.graph(g, stream=side):
             for f in fns:
                 f()
         g.replay()
@@ -182,9 +188,12 @@ def run_kernels(pk, pk_src):
         line["peaks"] = pk_src
         print(json.dumps(line), flush=True)
 
+    def want(section):
+        return only is None or only in section
+
     d, page = 128, 64
     # ---- decode attention (the position encoding and the cache write inside)
-    for B, nh, nkv, ctx in ((1, 32, 32, 512), (1, 32, 32, 4096), (8, 32, 32, 512), (8, 32, 32, 4096), (64, 32, 32, 512),
+    for B, nh, nkv, ctx in () if not want("attention_decode_ring") else ((1, 32, 32, 512), (1, 32, 32, 4096), (8, 32, 32, 512), (8, 32, 32, 4096), (64, 32, 32, 512),
                             (64, 32, 32, 4096), (8, 32, 8, 4096), (1, 32, 8, 32768), (16, 32, 8, 16384), (8, 40, 40, 4096)):
         per = -(-ctx // page)
         n_l = max(2, min(8, int(2e9 // (B * per * page * nkv * d * 4)) or 2))
@@ -205,19 +214,31 @@ def run_kernels(pk, pk_src):
     shapes = {"7B qkv": (12288, 4096), "7B o": (4096, 4096), "7B gate/up+act": (22016, 4096), "7B down": (4096, 11008),
               "7B head": (32000, 4096), "8B qkv": (6144, 4096), "8B gate/up+act": (28672, 4096), "8B down": (4096, 14336),
               "8B head": (128256, 4096), "13B qkv": (15360, 5120), "13B gate/up+act": (27648, 5120), "13B down": (5120, 13824)}
-    for name, (N, K) in shapes.items():
+    for name, (N, K) in shapes.items() if want("gemm_tc (decode)") else ():
         n_w = max(2, min(6, int(1.5e9 // (N * K * 2))))
         ws = [(torch.randn(N, K, device=dev) * 0.02).bfloat16() for _ in range(n_w)]
         for M in (1, 8, 16):
             x = torch.randn(M, K, device=dev).bfloat16()
-            if "act" in name:
-                us = graph_us([lambda w=w: ops.linear_gated(x, w) for w in ws])
+            # the kernels themselves with the engine's choice of K slices (the slices stay unreduced, as in a step)
+            if "act" in name and ops.gemm_tc_splits(M, N, K) == 1:
+                us = graph_us([lambda w=w: ops.gemm_bf16_tc_gated(x, w) for w in ws])
             else:
-                us = graph_us([lambda w=w: ops.linear(x, w, defer_reduce=True) for w in ws])
+                us = graph_us([lambda w=w: ops.gemm_bf16_tc(x, w, torch.float32, defer_reduce=True) for w in ws])
             emit("gemm_tc (decode)", f"{name}, {M} tokens", us, nbytes=N * K * 2)
         del ws
+    # ---- the float32 mode's product of a few rows (true float32: no tensor cores, one chain of FMAs per output)
+    for name, (N, K) in shapes.items() if want("gemm_f32 (decode)") else ():
+        if not name.startswith("7B"):
+            continue
+        n_w = max(2, min(4, int(1.5e9 // (N * K * 4))))
+        ws = [torch.randn(N, K, device=dev) * 0.02 for _ in range(n_w)]
+        for M in (1, 4, 8):
+            x = torch.randn(M, K, device=dev)
+            us = graph_us([lambda w=w: ops.gemm_f32(x, w) for w in ws])
+            emit("gemm_f32 (decode)", f"{name.replace('+act', '')}, {M} tokens", us, nbytes=N * K * 4)
+        del ws
     # ---- prompt attention
-    for T, nh, nkv in ((512, 32, 32), (2048, 32, 32), (2048, 32, 8), (8192, 32, 32), (16384, 32, 32), (16384, 32, 8)):
+    for T, nh, nkv in () if not want("attention_prefill_tc") else ((512, 32, 32), (2048, 32, 32), (2048, 32, 8), (8192, 32, 32), (16384, 32, 32), (16384, 32, 8)):
         n_pages = T // page
         kc = torch.randn(n_pages, nkv, page, d, device=dev).bfloat16()
         vc = torch.randn_like(kc)
@@ -230,7 +251,7 @@ def run_kernels(pk, pk_src):
         del kc, vc, qkv
     # ---- prompt-sized products on the SM-pair kernel, and the library beside them
     x = torch.randn(2048, 4096, device=dev).bfloat16()
-    for name, (N, K) in (("7B qkv", (12288, 4096)), ("7B gate/up+act", (22016, 4096)), ("7B down", (4096, 11008))):
+    for name, (N, K) in () if not want("gemm_tc2") else (("7B qkv", (12288, 4096)), ("7B gate/up+act", (22016, 4096)), ("7B down", (4096, 11008))):
         xx = x if K == 4096 else torch.randn(2048, K, device=dev).bfloat16()
         ws = [(torch.randn(N, K, device=dev) * 0.02).bfloat16() for _ in range(3)]
         gated = "act" in name
@@ -243,6 +264,8 @@ def run_kernels(pk, pk_src):
         emit("library (cuBLAS)" + (" + swiglu" if gated else ""), f"{name}, 2048 tokens", us, flops=2 * 2048 * N * K)
         del ws
     # ---- the memory-bound kernels of a prompt step (2,048 tokens of a 7B layer)
+    if not want("add_rmsnorm, rope_kv_write"):
+        return 0
     T, H, I, nh, nkv = 2048, 4096, 11008, 32, 32
     resid = [torch.randn(T, H, device=dev) for _ in range(4)]
     delta = [torch.randn(T, H, device=dev).bfloat16() for _ in range(4)]
@@ -327,6 +350,8 @@ def main():
     ap.add_argument("--context", type=int, default=CONTEXT, help="position at which the timed decode steps end")
     ap.add_argument("--kernels", action="store_true", help="beside the contract: the hot kernels one by one at "
                     "several sizes, one JSON line each")
+    ap.add_argument("--kernel", metavar="NAME", help="with --kernels: only the section whose name holds NAME "
+                    "(attention_decode_ring, gemm_tc (decode), gemm_f32 (decode), attention_prefill_tc, gemm_tc2, add_rmsnorm)")
     ap.add_argument("--scenario", metavar="B:MIN:MAX:NEW", help="beside the contract: B prompts of random ids with "
                     "lengths uniform in [MIN, MAX] (seeded) prefilled in one step of unequal lengths, then NEW tokens "
                     "each (or 'toN': until position N), through the Python entry point; 'config' = the workload of --model "
@@ -366,7 +391,7 @@ def main():
     B = args.batch
 
     if args.kernels:
-        return run_kernels(pk, pk_src)
+        return run_kernels(pk, pk_src, args.kernel)
     if args.scenario:
         return run_scenario(args, cfg, cfgd, model_name, L, fig, pk, pk_src)
 

@@ -68,12 +68,15 @@ namespace ops {
 enum class GemmBackend { Auto, TC, Library };
 // Which kernel runs the bfloat16 matrix products.  TC: the package's tcgen05 kernels for every
 // product they can take (K a multiple of 8): gemm_tc.cu up to 128 tokens, the SM-pair kernel
-// gemm_tc2.cu above; Library: cuBLAS; Auto (default): the tcgen05 kernel for decode batches of at
-// most 64 tokens, where its swapped, split-K form with weight prefetch across kernel boundaries is
-// faster than the library (the four products of a 7B layer, back to back: 74.8 against 89.5 us at
-// batch 1, 78.1 against 79.4 at batch 16, 85.0 against 88.1 at batch 64 with the activation's kernel
-// counted), and the library for larger ones; gate/up products of prompts from 512 tokens on run on
-// the SM-pair kernel with the activation as their epilogue.
+// gemm_tc2.cu above; Library: cuBLAS; Auto (default): the tcgen05 kernel for small decode batches (at
+// most 16 tokens), where its swapped, split-K form with weight prefetch across kernel boundaries is
+// faster than the library (74.8 against 89.5 us for the four products of a 7B layer at batch 1, 78.1
+// against 79.4 at batch 16), and the library for larger ones.  From 17 to 64 tokens the kernel alone
+// still matches the library (85.0 against 88.1 us at 64 tokens, back to back), but its float32 K
+// slices grow with the tokens and their readers (the norms, the fused attention) pay for them: whole
+// 7B decode steps at context 600 take 4.35 ms with the library and 4.47 ms with the kernel at batch
+// 24, 4.77 and 5.01 at batch 32, 5.86 and 6.17 at batch 48.  Gate/up products of prompts from 512
+// tokens on run on the SM-pair kernel with the activation as their epilogue.
 GemmBackend gemm_backend_from_name(const std::string& name);
 const char* gemm_backend_name(GemmBackend b);
 

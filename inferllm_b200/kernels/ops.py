@@ -658,6 +658,22 @@ def gemm_bf16_tc(x, w, out_dtype=torch.bfloat16, splits=None, defer_reduce=False
     return SplitKPartials(ws) if defer else out
 
 
+def gemm_bf16_tc_gated(x, w):
+    """silu(gate) * up of bfloat16 x [M <= 64, K] . w [2I, K]^T (rows 2i, 2i + 1: gate and up of output
+    i) -> [M, I] bfloat16, the activation applied to the accumulators (no split of K)."""
+    _need(x, "x", torch.bfloat16, 2)
+    _need(w, "w", torch.bfloat16, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or N % 2 or M > 64 or K % 8:
+        raise KernelError(f"gemm_bf16_tc_gated: x {tuple(x.shape)}, w {tuple(w.shape)}: at most 64 rows, K a multiple of 8, "
+                          "an even number of weight rows")
+    out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    _check(load().illm_gemm_bf16_tc_gated(_ptr(x), _ptr(w), _ptr(out), M, N, K, _ptr(tc_error_word(x.device)), _stream()),
+           "gemm_bf16_tc_gated")
+    return out
+
+
 def set_pdl(on: bool) -> None:
     """Programmatic dependent launch of the package's kernels (on by default)."""
     _b.lib().illm_set_pdl_enabled(1 if on else 0)

@@ -448,9 +448,9 @@ def test_random_batches_against_float32():
 
 @pytest.mark.parametrize("B", [17, 33, 64, 80])
 def test_decode_steps_of_many_sequences(B, tmp_path):
-    """One-token steps of 17, 33, 64 and 80 sequences: 17, 33 and 64 take the wider token tiles of the
-    package's split products, 80 the library's products (finished tensors instead of K slices into
-    the norms and into the fused attention kernel), and each batch size captures a graph of its own.  Every sequence has another
+    """One-token steps of 17, 33, 64 and 80 sequences: from 17 tokens on a decode step takes the
+    library's products (finished tensors instead of K slices into the norms and into the fused
+    attention kernel), and each batch size captures a graph of its own.  Every sequence has another
     length; all of them are checked against the float32 engine at every decoded position, and two
     of them (the shortest and the longest) against the plain implementation."""
     import plain_llama
@@ -482,9 +482,9 @@ def test_decode_steps_of_many_sequences(B, tmp_path):
 
 
 def test_batch_that_shrinks_across_the_kernel_switch(tmp_path):
-    """Seventy sequences of which eight end early, one per step, so that the live count falls from 70
-    to 62 while decoding: the step changes from the library's products to the package's split
-    product at 64 tokens, and every count replays or captures another graph.  All positions against
+    """Twenty sequences of which eight end early, one per step, so that the live count falls from 20
+    to 12 while decoding: the step changes from the library's products to the package's split
+    product at 16 tokens, and every count replays or captures another graph.  All positions against
     the float32 engine, the last request to end against the plain implementation."""
     import plain_llama
 
@@ -495,7 +495,7 @@ def test_batch_that_shrinks_across_the_kernel_switch(tmp_path):
     folder = str(tmp_path)
     write_random_model(config_from_dict(cfg), folder, 6, torch.bfloat16)
     rng = np.random.default_rng(3)
-    B = 70
+    B = 20
     lens = [int(rng.integers(5, 150)) for _ in range(B)]
     extra = [2 + i for i in range(8)] + [14] * (B - 8)   # requests 0..7 end after 2..9 single-token steps
     reqs = [rng.integers(0, 640, size=n + e).tolist() for n, e in zip(lens, extra)]
