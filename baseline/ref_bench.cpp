@@ -16,7 +16,8 @@
 //
 // Prints one JSON object: the wall time per decode_iter call over the last STEPS calls, the same by
 // the reference's own timer (decode_summary's "Total Model Compute Time", which sums the execute
-// calls of decode_iter, src/core/model_imp.cpp:55-64), and the time the context took to feed.
+// calls of decode_iter, src/core/model_imp.cpp:55-64), the time the context took to feed, and the
+// wall-clock times at which the timed calls began and ended.
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -42,6 +43,9 @@ static double compute_seconds(const std::string& summary) {
     return at == std::string::npos ? -1.0 : atof(summary.c_str() + at + strlen(key));
 }
 
+static double unix_s() {   // wall-clock time, so that the caller can pick the clock samples of the timed region
+    return std::chrono::duration<double>(std::chrono::system_clock::now().time_since_epoch()).count();
+}
 static double now_s() {
     return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
 }
@@ -101,12 +105,14 @@ int main(int argc, char** argv) {
 
     for (int i = 0; i < warmup; i++) model->decode_iter(token);
     const double own0 = compute_seconds(model->decode_summary());
+    const double unix0 = unix_s();
     const double t0 = now_s();
     for (int i = 0; i < steps; i++) model->decode_iter(token);
     const double wall = now_s() - t0;
+    const double unix1 = unix_s();
     const double own = compute_seconds(model->decode_summary()) - own0;
     printf("{\"device\": \"%s\", \"threads\": %d, \"context_tokens\": %d, \"feed_s\": %.4f, \"steps\": %d, "
-           "\"wall_ms_per_token\": %.4f, \"own_timer_ms_per_token\": %.4f}\n",
-           device.c_str(), threads, fed, t_feed, steps, wall * 1e3 / steps, own * 1e3 / steps);
+           "\"wall_ms_per_token\": %.4f, \"own_timer_ms_per_token\": %.4f, \"timed_begin_unix\": %.3f, \"timed_end_unix\": %.3f}\n",
+           device.c_str(), threads, fed, t_feed, steps, wall * 1e3 / steps, own * 1e3 / steps, unix0, unix1);
     return 0;
 }

@@ -195,4 +195,5 @@ def run(steps: int, warmup: int, layers: int = 4, context_tokens: int = 512, gpu
                 "note": "wall clock around decode_iter: token in and sampled token out on the host every step",
                 "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4 * SIZES_7B["vocab"]},
         "feed_context_s": res["feed_s"], "notes": notes,
+        "timed_window_unix": [res.get("timed_begin_unix"), res.get("timed_end_unix")],
     }

@@ -72,13 +72,13 @@ class ClockSampler:
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, device=0):
-        self.samples, self.proc, self.device = [], None, device
+        self.samples, self.times, self.proc, self.device = [], [], None, device
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -91,6 +91,7 @@ class ClockSampler:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) == 6 and parts[0].isdigit():
                 self.samples.append(parts)
+                self.times.append(time.time())
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -100,13 +101,20 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
 
-    def summary(self):
-        if not self.samples:
+    def summary(self, begin=None, end=None):
+        """Median SM clock and the throttle reasons seen; `begin`, `end` (wall-clock seconds): only
+        the samples taken between them, if there are at least two (a sample is up to a period late)."""
+        samples = self.samples
+        if begin is not None and end is not None:
+            inside = [s for s, t in zip(self.samples, self.times) if begin <= t <= end + 0.1]
+            if len(inside) >= 2:
+                samples = inside
+        if not samples:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
-        mhz = sorted(int(s[0]) for s in self.samples)
+        mhz = sorted(int(s[0]) for s in samples)
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(self.samples[0][1]), "reasons": reasons,
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(samples[0][1]), "reasons": reasons,
                 "samples": len(mhz)}
 
 
@@ -368,7 +376,8 @@ def main():
         with ClockSampler() as cs:
             line = reference_arm.run(args.steps, args.warmup, layers=REF_LIKE_LAYERS, gpu_visible=gpu)
         if "unavailable" not in line:
-            line["clocks"] = cs.summary()
+            # the clocks of the timed calls alone (the run also writes and loads a model file)
+            line["clocks"] = cs.summary(*line.pop("timed_window_unix", (None, None)))
             line["gpu_launches"] = 0        # none of this repository's kernels run in the reference arm
         print(json.dumps(line))
         return 0
