@@ -28,6 +28,10 @@ Device::Device(int ordinal, cudaStream_t stream) : ordinal_(ordinal) {
     cudaDeviceProp prop;
     check_cuda(cudaGetDeviceProperties(&prop, ordinal), "cudaGetDeviceProperties");
     n_sms_ = prop.multiProcessorCount;
+    int mem_khz = 0, bus_bits = 0;
+    if (cudaDeviceGetAttribute(&mem_khz, cudaDevAttrMemoryClockRate, ordinal) == cudaSuccess &&
+        cudaDeviceGetAttribute(&bus_bits, cudaDevAttrGlobalMemoryBusWidth, ordinal) == cudaSuccess && mem_khz > 0 && bus_bits > 0)
+        stream_bytes_per_us_ = 0.86 * 2.0 * (double)mem_khz * 1e3 * ((double)bus_bits / 8.0) / 1e6;
     if (prop.major != 10)
         throw EngineError(std::string("GPU ") + prop.name + " has compute capability " + std::to_string(prop.major) + "." +
                           std::to_string(prop.minor) + ": the kernels of inferllm_b200 are built for sm_100a (B200) only");

@@ -43,6 +43,10 @@ public:
 
     int ordinal() const { return ordinal_; }
     int n_sms() const { return n_sms_; }
+    // Bytes per microsecond that a streaming kernel reads from device memory: 0.86 of the product of the
+    // memory clock, the bus width and the double data rate, which is what a copy reaches on this kind of
+    // memory (6.6e6 on a B200).  The policies that weigh a kernel's stream against its fixed costs use it.
+    double stream_bytes_per_us() const { return stream_bytes_per_us_; }
     cudaStream_t stream() const { return stream_; }
     void set_stream(cudaStream_t s);
     // Ordering against another stream of the same device (a caller that exchanges device memory with
@@ -90,6 +94,7 @@ private:
     struct Block { char* base; size_t size, used; };
     struct Lane { std::vector<Block> blocks; size_t cur = 0; };
     int ordinal_, n_sms_ = 148;
+    double stream_bytes_per_us_ = 6.6e6;
     cudaStream_t stream_ = nullptr;
     bool own_stream_ = false;
     Lane lanes_[kLanes];

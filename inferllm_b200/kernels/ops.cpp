@@ -67,10 +67,10 @@ int gemm_tc_splits(long long M, long long N, long long K, int n_sms) {
     return (int)ceil_div(k_iters, per);          // every slice owns at least one 64-wide piece of K
 }
 
-int attention_decode_ring_splits(long long T, int n_kv_heads, long long max_len, int head_dim, int n_sms) {
+int attention_decode_ring_splits(long long T, int n_kv_heads, long long max_len, int head_dim, int n_sms, double stream_bytes_per_us) {
     const long long pairs = std::max<long long>(1, T * n_kv_heads), tiles = std::max<long long>(1, ceil_div(max_len, 64));
     const long long slots = 2LL * n_sms;
-    const double stream_us = (double)pairs * (double)max_len * head_dim * 4 / 6.6e6;
+    const double stream_us = (double)pairs * (double)max_len * head_dim * 4 / stream_bytes_per_us;
     int best = 1;
     double best_us = INFINITY;
     for (long long n = 1; n <= std::min<long long>(tiles, kRingDecodeMaxSplits); n++) {
@@ -437,7 +437,7 @@ Mat attention_decode_ring(Device& dev, const MatOrPartials& in, const KVView& kv
     Mat out = new_mat_exact(dev, T, (long long)g.n_heads * g.head_dim, DType::BF16);
     for (long long t0 = 0; t0 < T; t0 += 65535) {
         const long long t1 = std::min(T, t0 + 65535);
-        const int n = splits > 0 ? splits : attention_decode_ring_splits(t1 - t0, g.n_kv_heads, max_len, g.head_dim, dev.n_sms());
+        const int n = splits > 0 ? splits : attention_decode_ring_splits(t1 - t0, g.n_kv_heads, max_len, g.head_dim, dev.n_sms(), dev.stream_bytes_per_us());
         float *part_acc = nullptr, *part_ml = nullptr;
         if (n > 1) {
             part_acc = dev.alloc_n<float>((size_t)(t1 - t0) * g.n_heads * n * g.head_dim);

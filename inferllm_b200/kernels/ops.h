@@ -104,7 +104,8 @@ int gemm_tc_splits(long long M, long long N, long long K, int n_sms);
 // bound by what one SM can take in), so a grid a little larger than one wave is the worst and one of
 // many waves is fine again.  Splits cost their partial results and the merge (2.5 us and 0.7 us per
 // split), every wave about 1 us of start-up.  At most one split per 64-key tile and at most 32.
-int attention_decode_ring_splits(long long T, int n_kv_heads, long long max_len, int head_dim, int n_sms);
+int attention_decode_ring_splits(long long T, int n_kv_heads, long long max_len, int head_dim, int n_sms,
+                                 double stream_bytes_per_us = 6.6e6);
 bool attention_decode_ring_supported(DType dtype, int nh, int nkv, int d, int page_size);
 bool attention_decode_supported(DType dtype, int nh, int nkv, int d, int page_size);
 bool attention_decode_gqa_supported(DType dtype, int nh, int nkv, int d);
