@@ -78,7 +78,11 @@ static int run(int argc, char** argv) {
         if (!rec.is_object() || !rec.has("step")) throw EngineError("a line of the trace lacks 'step'");
         const std::string step = rec.at("step").is_string() ? rec.at("step").as_string() : std::to_string(rec.at("step").as_int());
         std::vector<StepItem> items;
-        for (const Json& e : rec.at("entries").items()) {
+        const Json none = Json::parse("[]");       // a key that is left out means "nothing"
+        const Json& entries = rec.has("entries") ? rec.at("entries") : none;
+        const Json& ending = rec.has("end") ? rec.at("end") : none;
+        if (!entries.is_array() || !ending.is_array()) throw EngineError("'entries' and 'end' of a trace line must be lists");
+        for (const Json& e : entries.items()) {
             if (!e.is_object() || !e.has("id") || !e.at("tokens").is_array()) throw EngineError("an entry of the trace lacks 'id' or 'tokens'");
             const std::string id = e.at("id").is_string() ? e.at("id").as_string() : e.at("id").dump();
             auto it = slots.find(id);
@@ -86,7 +90,8 @@ static int run(int argc, char** argv) {
             StepItem item;
             item.slot = it->second;
             for (const Json& t : e.at("tokens").items()) item.tokens.push_back((int)t.as_int());
-            for (const Json& w : e.at("want").items()) item.want.push_back((int)w.as_int());
+            if (e.has("want"))
+                for (const Json& w : e.at("want").items()) item.want.push_back((int)w.as_int());
             items.push_back(std::move(item));
         }
         if (!items.empty()) {
@@ -100,7 +105,7 @@ static int run(int argc, char** argv) {
                 fclose(f);
             }
         }
-        for (const Json& id : rec.at("end").items()) {
+        for (const Json& id : ending.items()) {
             const std::string key = id.is_string() ? id.as_string() : id.dump();
             auto it = slots.find(key);
             if (it != slots.end()) {

@@ -129,3 +129,41 @@ def test_steps_without_wanted_logits_write_no_file(model_folders, tmp_path):
              {"step": 9, "entries": [{"id": "x", "tokens": [4], "want": [0]}], "end": ["x"]}]
     out = replay(model_folders["A"], "float32", steps, str(tmp_path), 64)
     assert list(out) == [9] and out[9].shape == (1, 256)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_wanted_places_in_any_order_many_requests_and_two_batches_alive(dtype, model_folders, plain_logits, tmp_path):
+    """What a trace may also hold: wanted places out of order and named twice (the rows follow `want`),
+    an entry without `want` and a line without `end`, a hundred requests alive at once (the cache has a
+    slot per page), and a second batch that starts while the first is still decoding."""
+    name = "A"
+    n_req = 100
+    lens = [3 + (7 * i) % 29 for i in range(n_req)]
+    reqs = {f"r{i}": random_prompt(name, lens[i] + 2, 900 + i) for i in range(n_req)}
+    first, second = [f"r{i}" for i in range(60)], [f"r{i}" for i in range(60, n_req)]
+
+    def prompt_entry(rid, i):
+        n = len(reqs[rid]) - 2
+        want = [n - 1, 0, n - 1] if i % 3 == 0 else ([n - 1] if i % 3 == 1 else None)
+        e = {"id": rid, "tokens": reqs[rid][:n]}
+        if want is not None:
+            e["want"] = want
+        return e
+
+    steps = [{"step": 0, "entries": [prompt_entry(r, i) for i, r in enumerate(first)]},              # no "end"
+             {"step": 1, "entries": [{"id": r, "tokens": [reqs[r][-2]], "want": [0]} for r in first], "end": []},
+             {"step": 2, "entries": [prompt_entry(r, i) for i, r in enumerate(second)], "end": []},  # the first batch still lives
+             {"step": 3, "entries": [{"id": r, "tokens": [reqs[r][-1]], "want": [0]} for r in first], "end": first},
+             {"step": 4, "entries": [{"id": r, "tokens": [reqs[r][-2]], "want": [0]} for r in second], "end": second[:5]},
+             {"step": 5, "entries": [{"id": r, "tokens": [reqs[r][-1]], "want": [0]} for r in second[5:]], "end": second[5:]}]
+    out = replay(model_folders[name], dtype, steps, str(tmp_path), 64 * n_req)
+    for st in steps:
+        row = 0
+        for e in st["entries"]:
+            rid = e["id"]
+            ref = plain_logits(name, reqs[rid])
+            start = {0: 0, 2: 0, 1: len(reqs[rid]) - 2, 4: len(reqs[rid]) - 2, 3: len(reqs[rid]) - 1, 5: len(reqs[rid]) - 1}[st["step"]]
+            for w in e.get("want", []):
+                assert_close(out[st["step"]][row][None], ref[start + w][None], dtype, f"step {st['step']} {rid} place {w}")
+                row += 1
+        assert row == out[st["step"]].shape[0]
