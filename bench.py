@@ -356,6 +356,8 @@ def main():
     ap.add_argument("--gemm", default="auto", choices=["auto", "tc", "library"])
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels without programmatic dependent launch")
     ap.add_argument("--context", type=int, default=CONTEXT, help="position at which the timed decode steps end")
+    ap.add_argument("--timeline", action="store_true", help="with --only decode: print when every kernel of one "
+                    "step starts and ends inside the captured graph")
     ap.add_argument("--kernels", action="store_true", help="beside the contract: the hot kernels one by one at "
                     "several sizes, one JSON line each")
     ap.add_argument("--kernel", metavar="NAME", help="with --kernels: only the section whose name holds NAME "
@@ -435,8 +437,8 @@ def main():
         return e0.elapsed_time(e1) / n
 
     # ---- decode: `batch` sequences, timed steps end at position `ctx_end`
-    def decode_run(engine, batch, ctx_end, steps, warm):
-        start = ctx_end - steps - warm
+    def decode_run(engine, batch, ctx_end, steps, warm, timeline=False):
+        start = ctx_end - steps - warm - (3 if timeline else 0)     # the timeline takes three steps of its own
         slots = [engine.new_sequence() for _ in range(batch)]
         per_step = max(1, 8192 // start)                  # prompts go in steps of about 8k tokens
         for i in range(0, batch, per_step):
@@ -448,6 +450,8 @@ def main():
 
         for _ in range(warm):
             one()
+        if timeline:
+            print_timeline(one)
         before = ops.launch_count()
         ms = timed(one, steps)
         launches = ops.launch_count() - before
@@ -455,12 +459,31 @@ def main():
             engine.end_sequence(s)
         return ms, launches
 
+    def print_timeline(one):
+        """Start and duration of every kernel of one step inside its captured graph, from the driver's
+        activity records (torch.profiler over CUPTI; no replay, no serialisation: the kernels overlap as
+        they do in a timed run, each some microseconds slower for the tracing)."""
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(3):
+                one()
+            torch.cuda.synchronize()
+        ev = sorted((e for e in prof.events() if e.device_type.name == "CUDA"), key=lambda e: e.time_range.start)
+        last = ev[-(len(ev) // 3):]                 # the third step
+        t0, latest = last[0].time_range.start, last[0].time_range.start
+        print("   start     ends  since the latest end before it   kernel")
+        for e in last:
+            start, end = e.time_range.start - t0, e.time_range.end - t0
+            print(f"{start:8.1f} {end:8.1f}   {e.time_range.end - max(latest, e.time_range.start):+7.1f} us   {e.name[:64]}")
+            latest = max(latest, e.time_range.end)
+        print(f"step: {latest - t0:.1f} us")
+
     def hbm_frac(figures, batch, ctx_end, steps, ms):
         nbytes = figures["weight_bytes"] + batch * (ctx_end - steps // 2) * figures["kv_bytes_per_token"]
         return nbytes, nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]
 
     if args.only == "decode":
-        ms, launches = decode_run(eng, B, args.context, K, W)
+        ms, launches = decode_run(eng, B, args.context, K, W, timeline=args.timeline)
         print(json.dumps({"only": "decode", "batch": B, "layers": L, "context": args.context,
                           "ms_per_step": round(ms, 4), "gpu_launches": launches}))
         return 0
