@@ -264,6 +264,27 @@ def test_result_does_not_depend_on_the_slot_or_on_old_cache_contents(model_folde
     eng.check_device_errors()
 
 
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_bfloat16_steps_give_the_same_bits_every_time(name, model_folders):
+    """No sum of the bfloat16 kernels depends on timing (split products and split attention are added
+    up in a fixed order, nothing is accumulated with atomics): the same batch, replayed in the same
+    engine and in a second engine, gives the same logits bit for bit, through prompts of unequal
+    lengths, eager first steps, captured graphs and their replays."""
+    lens = [LENGTHS[name][0], 70, 33]
+    reqs = [random_prompt(name, n, 40 + i) for i, n in enumerate(lens)]
+    pre = [lens[0] - 20, 40, 5]
+    runs = []
+    for _ in range(2):
+        eng = make_engine(model_folders[name], "bfloat16", max_tokens=64 * 16, max_batch=3)
+        for _ in range(2):
+            runs.append(in_batches(eng, reqs, pre, [[0, 1, 2]]))
+        eng.check_device_errors()
+        del eng
+    for other in runs[1:]:
+        for r in range(3):
+            assert np.array_equal(runs[0][r], other[r]), f"request {r} differs between two runs of the same batch"
+
+
 def test_refusals(model_folders):
     eng = make_engine(model_folders["A"], "float32", max_tokens=128, max_batch=2)
     s = eng.new_sequence()
