@@ -153,6 +153,28 @@ def build(force: bool = False, verbose: bool = True, extra_flags=()) -> str:
     nvcc, cxx = find_nvcc(), find_cxx()
     inc = os.path.join(cuda_home(nvcc), "include")
     out = build_dir()
+    # one builder per folder at a time: a second process that starts meanwhile waits and then finds the
+    # finished library instead of compiling into the same object files
+    import fcntl
+    lock = open(os.path.join(out, ".lock"), "w")
+    try:
+        fcntl.flock(lock, fcntl.LOCK_EX | fcntl.LOCK_NB)
+    except OSError:
+        if verbose:
+            _log("another process is compiling the library; waiting for it")
+        fcntl.flock(lock, fcntl.LOCK_EX)
+    try:
+        if not force:
+            lib = current_library()
+            if lib:
+                return lib
+        return _build_locked(nvcc, cxx, inc, out, force, verbose, extra_flags)
+    finally:
+        fcntl.flock(lock, fcntl.LOCK_UN)
+        lock.close()
+
+
+def _build_locked(nvcc, cxx, inc, out, force, verbose, extra_flags) -> str:
     headers = _headers_hash()
     srcs = sources()
     t0 = time.time()
