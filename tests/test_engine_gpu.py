@@ -378,6 +378,62 @@ def test_drawn_configurations(index, tmp_path):
         del eng
 
 
+@pytest.mark.parametrize("seed", range(10))
+def test_drawn_configurations_pages_and_batches(seed, tmp_path):
+    """Ten more draws in which everything varies together: the sizes as above, the page size (16 to 128),
+    the number of requests (3 to 7, or 17 to 40 so that single-token steps take the library's products),
+    their lengths, how much of each is its prompt, how the requests are cut into batches that follow one
+    another in the same slots, the length of the tail decoded one by one, and whether freed pages are
+    poisoned; both precisions against the plain implementation, float32 bit for bit between cuttings."""
+    import plain_llama
+
+    from inferllm_b200 import config_from_dict, write_random_model
+    rng = np.random.default_rng(77000 + seed)
+    d = int(rng.choice([16, 32, 48, 64, 64, 80, 96, 112, 128, 128, 144, 192, 256]))
+    nkv, group = int(rng.integers(1, 6)), int(rng.choice([1, 1, 2, 3, 4, 5, 8]))
+    maxpos = int(rng.choice([96, 160, 257, 400]))
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=int(rng.choice([24, 36, 72, 100, 136, 200, 264, 90, 54, 256, 512])),
+               num_hidden_layers=int(rng.integers(1, 4)), num_attention_heads=nkv * group, num_key_value_heads=nkv, head_dim=d,
+               intermediate_size=int(rng.integers(17, 600)), vocab_size=int(rng.integers(33, 3000)),
+               rope_theta=float(rng.choice([1e4, 5e5, 1e6, 777.0, 123456.7])),
+               rms_norm_eps=float(rng.choice([1e-5, 1e-6, 2e-4, 1e-3])), max_position_embeddings=maxpos,
+               tie_word_embeddings=bool(rng.integers(0, 2)), eos_token_id=2)
+    page = int(rng.choice([16, 32, 64, 64, 128]))
+    what = f"draw {seed}, pages of {page}: " + ", ".join(f"{k}={cfg[k]}" for k in (
+        "hidden_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads", "head_dim", "intermediate_size",
+        "vocab_size", "max_position_embeddings", "tie_word_embeddings"))
+    folder = str(tmp_path)
+    write_random_model(config_from_dict(cfg), folder, 7000 + seed, torch.bfloat16)
+    pcfg, pw = plain_llama.load_weights(folder)
+    n_req = int(rng.integers(3, 8)) if seed % 3 else int(rng.integers(17, 41))
+    lens = [int(rng.integers(1, (maxpos if n_req < 10 else min(maxpos, 120)) + 1)) for _ in range(n_req)]
+    lens[0] = maxpos
+    reqs = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in lens]
+    refs = [plain_llama.forward(pcfg, pw, ids) for ids in reqs]
+    pre = [int(rng.integers(1, n + 1)) for n in lens]
+    pre[0] = max(1, maxpos - int(rng.integers(1, 40)))
+    order = list(range(n_req))
+    rng.shuffle(order)
+    cut = sorted(set([0, n_req] + [int(x) for x in rng.integers(1, n_req, size=2)]))
+    batches = [order[a:b] for a, b in zip(cut[:-1], cut[1:])]
+    for dtype in DTYPES:
+        eng = make_engine(folder, dtype, max_tokens=sum(-(-n // page) * page for n in lens) + 2 * page, page_size=page,
+                          max_batch=max(len(b) for b in batches), poison=bool(rng.integers(0, 2)))
+        w = whole(eng, reqs[0])
+        assert_close(w, refs[0], dtype, what + " whole")
+        tail = int(rng.integers(1, min(33, maxpos)))
+        t = tail_one_by_one(eng, reqs[0], tail=tail)
+        assert_close(t, refs[0], dtype, what + f" last {tail} one by one")
+        got = in_batches(eng, reqs, pre, batches)
+        for r in range(n_req):
+            assert_close(got[r], refs[r], dtype, what + f" request {r} ({lens[r]} tokens, prompt of {pre[r]}) in {batches}")
+        if dtype == "float32":
+            assert np.array_equal(w, t) and np.array_equal(w, got[0]), what + ": float32 logits differ between cuttings"
+        eng.check_device_errors()
+        eng.cache.check()
+        del eng
+
+
 def test_layers_of_real_width_bfloat16_against_float32():
     """Two layers with the widths of an 8B model (4096 wide, 32 heads over 8 KV heads of 128, a
     14336-wide feed-forward, 128256 words): the bfloat16 engine with its tensor-core kernels at the
